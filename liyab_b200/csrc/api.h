@@ -340,6 +340,63 @@ int lb_expert_product(int dtype, int gated, const void* a, int64_t lda, const vo
 int lb_expert_product_set_plain(int on);
 int lb_expert_combine(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, int n_rows, int width, int top, void* stream);
 
+/* lb_matrix_memory / lb_matrix_memory_pieces for heads that share queries and keys in groups: head h reads the query and key row
+ * (h / qk_share); both also take the third kind of recurrence: decay, zi null and zf the log of keep itself, a number a token and head
+ * (take = 1, no normaliser). */
+int lb_matrix_memory_shared(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                            const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
+                            int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
+                            float k_scale, float cap, int chunked, int qk_share, void* stream);
+int lb_matrix_memory_pieces_shared(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                                   const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
+                                   int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq, int n_head, int dim, int vdim, int value_tile,
+                                   float q_scale, float k_scale, float cap, float* scratch, int qk_share, void* stream);
+
+/* x[t,:] = table[tokens[t],:] * scale + e(positions[t]) with e[2i] = sin(pos w_i), e[2i+1] = cos(pos w_i), w_i = freq2[2i] + freq2[2i+1]
+ * (a frequency as the sum of two floats); with `gain` (float [width]) the row is then divided by its root mean square and multiplied by it. */
+int lb_embed_sinusoid(int dtype, const int32_t* tokens, const int32_t* positions, const void* table, const float* freq2, const float* gain, float* x,
+                      int n_tokens, int width, float scale, float eps, void* stream);
+
+/* lb_paged_attention_generic with a penalty by distance: `distance` holds r1 [n_head] then r2 [n_head], and the score of the key at
+ * distance d loses r1 ln(1 + r2 d); null: none. */
+int lb_paged_attention_generic_biased(int dtype, const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq, const int32_t* positions,
+                                      const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_tokens, int n_head,
+                                      int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance, void* stream);
+
+/* lb_qk_norm_store with a temperature on the queries: with temp_every > 0 every query value of the token at position p is multiplied by
+ * 1 + temp_coef ln(floor((p + 1) / temp_every) + 1). */
+int lb_qk_norm_store_tempered(int dtype, const float* proj, int64_t ld, int q_off, int k_off, int v_off, const float* q_weight, const float* k_weight,
+                              void* q_out, int64_t ldq, void* cache, const int32_t* slot_mapping, int n_tokens, int n_head, int n_kv_head, int dim,
+                              int vdim, int padded, int page_size, int norm, float eps, const int32_t* positions, float temp_coef, int temp_every,
+                              void* stream);
+
+/* lb_gated_act with every kind of gate: 0 sigmoid, 1 silu, 2 GELU (tanh form), 3 relu, 4 the capped form with (alpha, limit):
+ * g' = min(g, limit), u' = clamp(u, -limit, limit), mid = g' sigmoid(alpha g') (u' + 1). */
+int lb_gated_act_kind(int out_dtype, const float* gu, int64_t ld, void* mid, int64_t ldm, int n_rows, int inner, int act, float alpha, float limit,
+                      void* stream);
+
+/* The router with a bias (float [n_experts], added to the sums before the choice); the experts' products with every kind of gate and,
+ * with `weights` null, no weight on the experts' input; the sum of a row's results each times its weight. */
+int lb_router_topk_biased(int dtype, const void* h, int64_t ldh, const void* router, const float* bias, int32_t* ids, float* weights, int n_rows,
+                          int n_experts, int width, int top, int softmax, int renormalise, void* stream);
+int lb_expert_product_kind(int dtype, int gated, const void* a, int64_t lda, const void* w, int64_t expert_stride, const int32_t* offsets,
+                           const int32_t* pair_at, const float* weights, void* out, int64_t ldo, int n_pairs, int n_experts, int n, int k, int top, int act,
+                           float alpha, float limit, void* stream);
+int lb_expert_combine_weighted(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, const float* weights, int n_rows, int width,
+                               int top, void* stream);
+
+/* The pieces around a state space per head (see state_space.cu).  proj: float rows [z | x B C | dt] with the convolution's channels at
+ * column xbc_off and dt at dt_off; taps [channels, n_taps]; state: + slot * slot_stride floats, [n_taps - 1][channels];
+ * out rows: [x (n_head vdim) | B C (group_values) | dt x (n_head vdim) | -exp(a_log) dt (n_head)].  decode_only: every request brings one
+ * row, whose inputs enter the state in the same launch. */
+int lb_ssm_prepare(const float* proj, int64_t ld, int xbc_off, int dt_off, const float* taps, const float* tap_bias, const float* dt_bias,
+                   const float* a_log, float* state, int64_t slot_stride, const int32_t* tok_seq, const int32_t* q_start, const int32_t* slots, float* out,
+                   int64_t ldo, int n_tokens, int n_seq, int n_head, int vdim, int group_values, int n_taps, int decode_only, void* stream);
+/* out = (o + skip_gain[c / head] * skip) * silu(z), cut into `groups` equal parts each over its own root mean square, times weight;
+ * skip, z and weight may be null. */
+int lb_gated_group_norm(int out_dtype, const float* o, int64_t ldo, const float* skip, int64_t lds, const float* skip_gain, int head, const float* z,
+                        int64_t ldz, const float* weight, void* out, int64_t ld_out, int n_rows, int width, int groups, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

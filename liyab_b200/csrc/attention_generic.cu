@@ -99,7 +99,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
                                const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions,
                                const int32_t* __restrict__ block_table, int table_stride, T* __restrict__ out,
                                int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
-                               int page_size, float scale, int window) {
+                               int page_size, float scale, int window, const float* __restrict__ distance) {
     extern __shared__ float smem[];
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
@@ -109,6 +109,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
     const int kvh = h / (n_head / n_kv_head);
     const int pos = positions[t];
     const int32_t* table = block_table + (size_t)tok_seq[t] * table_stride;
+    // The head's pair (r1, r2) of the penalty by distance; r1 = 0 without one.
+    const float r1 = distance != nullptr ? distance[h] : 0.0f, r2 = distance != nullptr ? distance[n_head + h] : 0.0f;
 
     const int tile_stride = head_dim + 1;
     float* q_s = smem + (size_t)warp * (head_dim + kTile * tile_stride + kTile);
@@ -143,6 +145,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
             const float* krow = tile + lane * tile_stride;
             for (int d = 0; d < head_dim; ++d) dot = fmaf(q_s[d], krow[d], dot);
             s = dot * scale;
+            if (distance != nullptr) s -= lb_distance_penalty(r1, r2, pos - (j0 + lane));
         }
         const float m_new = fmaxf(m, lb_warp_max(s));
         const float p = lane < n_keys ? expf(s - m_new) : 0.0f;
@@ -228,7 +231,7 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
                                const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions,
                                const int32_t* __restrict__ block_table, int table_stride, float* __restrict__ out,
                                int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
-                               int page_size, float scale, int window) {
+                               int page_size, float scale, int window, const float* __restrict__ distance) {
     extern __shared__ __align__(16) float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const int pair = blockIdx.x;
@@ -236,6 +239,8 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
     const int kvh = h / (n_head / n_kv_head);
     const int pos = positions[t];
     const int32_t* table = block_table + (size_t)tok_seq[t] * table_stride;
+    // The head's pair (r1, r2) of the penalty by distance; r1 = 0 without one.
+    const float r1 = distance != nullptr ? distance[h] : 0.0f, r2 = distance != nullptr ? distance[n_head + h] : 0.0f;
 
     const int tile_stride = head_dim + 4;
     float* q_s = smem + (size_t)warp * (head_dim + 2 * kTile * tile_stride + kTile + 2 * kTile);
@@ -291,6 +296,7 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
                 dot = fmaf(qq.w, kq.w, dot);
             }
             s = dot * scale;
+            if (distance != nullptr) s -= lb_distance_penalty(r1, r2, pos - (j0 + lane));
         }
         const float m_new = fmaxf(m, lb_warp_max(s));
         const float p = lane < n_keys ? expf(s - m_new) : 0.0f;
@@ -362,7 +368,7 @@ int warps_for(int head_dim) {
 template <typename T>
 int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq, const int32_t* positions,
            const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_tokens, int n_head,
-           int n_kv_head, int head_dim, int page_size, float scale, int window, cudaStream_t s) {
+           int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance, cudaStream_t s) {
     const int warps = warps_for(head_dim);
     const size_t smem = (size_t)warps * (head_dim + kTile * (head_dim + 1) + kTile + head_dim + 2) * sizeof(float);
     static size_t configured = 0;   // largest dynamic shared memory asked for so far
@@ -384,14 +390,14 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* to
             }
             LB_CHECK_CUDA(lb_launch_overlapped(paged_attention_f32_few_kernel, dim3((unsigned)pairs), dim3(warps * 32), few, s, 
                 (const float*)q, q_stride, (const float*)cache, tok_seq, positions, block_table, table_stride, (float*)out, out_stride,
-                n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window));
+                n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance));
             LB_CHECK_LAUNCH();
             return LB_OK;
         }
     }
     LB_CHECK_CUDA(lb_launch_overlapped(paged_attention_generic_kernel<T>, dim3((unsigned)pairs), dim3(warps * 32), smem, s, 
         (const T*)q, q_stride, (const T*)cache, tok_seq, positions, block_table, table_stride, (T*)out, out_stride,
-        n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window));
+        n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
@@ -403,6 +409,14 @@ extern "C" int lb_paged_attention_generic(int dtype, const void* q, int64_t q_st
                                           const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
                                           int n_tokens, int n_head, int n_kv_head, int head_dim, int page_size,
                                           float scale, int window, void* stream) {
+    return lb_paged_attention_generic_biased(dtype, q, q_stride, cache, tok_seq, positions, block_table, table_stride, out, out_stride, n_tokens, n_head,
+                                             n_kv_head, head_dim, page_size, scale, window, nullptr, stream);
+}
+
+extern "C" int lb_paged_attention_generic_biased(int dtype, const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq,
+                                                 const int32_t* positions, const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
+                                                 int n_tokens, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window,
+                                                 const float* distance, void* stream) {
     LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_kv_head > 0 && page_size > 0, "attention: bad sizes");
     LB_CHECK_ARG(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
     LB_CHECK_ARG(head_dim > 0 && head_dim <= kMaxHeadDim, "attention: head_dim %d is outside (0, %d]", head_dim,
@@ -411,9 +425,9 @@ extern "C" int lb_paged_attention_generic(int dtype, const void* q, int64_t q_st
     auto s = static_cast<cudaStream_t>(stream);
     if (dtype == LB_F32)
         return launch<float>(q, q_stride, cache, tok_seq, positions, block_table, table_stride, out, out_stride,
-                             n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, s);
+                             n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance, s);
     if (dtype == LB_BF16)
         return launch<__nv_bfloat16>(q, q_stride, cache, tok_seq, positions, block_table, table_stride, out,
-                                     out_stride, n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, s);
+                                     out_stride, n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance, s);
     return lb_fail(LB_ERR_INVALID_ARGUMENT, "attention: unknown dtype %d", dtype);
 }

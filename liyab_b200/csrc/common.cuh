@@ -109,6 +109,9 @@ __host__ __device__ __forceinline__ int lb_first_visible(int pos, int window) {
     return 0;
 }
 
+// What a score loses by the distance between query and key, for heads that carry the pair (r1, r2): r1 ln(1 + r2 distance).
+__device__ __forceinline__ float lb_distance_penalty(float r1, float r2, int distance) { return r1 * logf(fmaf(r2, (float)distance, 1.0f)); }
+
 __device__ __forceinline__ float lb_to_float(float v) { return v; }
 __device__ __forceinline__ float lb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 
@@ -185,6 +188,20 @@ __device__ __forceinline__ float lb_activate(float x, int act) {
 __device__ __forceinline__ float lb_activate(float x, int act, const lb_act_pair& p) {
     if (act == LB_ACT_XIELU) return lb_xielu(x, p.a, p.b);
     return lb_activate(x, act);
+}
+
+// The two halves of a gated feed-forward meet: act(g) * u.  Kinds: 0 sigmoid, 1 silu, 2 GELU (tanh form), 3 relu, and 4, the capped
+// form with its two numbers (alpha, limit): g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1).
+enum lb_gate_kind : int { LB_GATE_SIGMOID = 0, LB_GATE_SILU = 1, LB_GATE_GELU_TANH = 2, LB_GATE_RELU = 3, LB_GATE_CAPPED = 4 };
+__device__ __forceinline__ float lb_gated_pair(float g, float u, int kind, float alpha, float limit) {
+    if (kind == LB_GATE_CAPPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+    }
+    const float sg = 1.0f / (1.0f + expf(-g));
+    const float a = kind == LB_GATE_SILU ? g * sg : kind == LB_GATE_GELU_TANH ? lb_gelu_tanh(g) : kind == LB_GATE_RELU ? fmaxf(g, 0.0f) : sg;
+    return a * u;
 }
 
 template <typename... Params, typename... Args>

@@ -84,6 +84,59 @@ extern "C" int lb_embed_positions(int dtype, const int32_t* tokens, const int32_
     return LB_OK;
 }
 
+// x[t, :] = table[token[t], :] * scale + e(pos[t]), e[2i] = sin(pos w_i), e[2i + 1] = cos(pos w_i); then, with a gain, the row over its
+// root mean square times the gain.  w_i arrives as two floats whose sum is the frequency to about 48 bits (freq2[2i] + freq2[2i + 1]):
+// the angle's leading part pos * hi is rounded once, what that rounding dropped and pos * lo enter as a first-order correction of
+// sine and cosine, so the angle of a far position is as good as that of a near one.
+template <typename T>
+__global__ void __launch_bounds__(256) embed_sinusoid_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ pos, const T* __restrict__ table,
+                                                             const float* __restrict__ freq2, const float* __restrict__ gain, float* __restrict__ x,
+                                                             int width, float scale, float eps) {
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const T* row = table + (size_t)tokens[t] * width;
+    const float p = (float)pos[t];
+    float* out = x + (size_t)t * width;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; 2 * i < width; i += blockDim.x) {
+        const float hi = freq2[2 * i], lo = freq2[2 * i + 1];
+        const float a = p * hi, r = fmaf(p, hi, -a) + p * lo;
+        float sn, cs;
+        sincosf(a, &sn, &cs);
+        const float v0 = fmaf(lb_to_float(row[2 * i]), scale, fmaf(r, cs, sn));
+        out[2 * i] = v0;
+        ss = fmaf(v0, v0, ss);
+        if (2 * i + 1 < width) {
+            const float v1 = fmaf(lb_to_float(row[2 * i + 1]), scale, fmaf(-r, sn, cs));
+            out[2 * i + 1] = v1;
+            ss = fmaf(v1, v1, ss);
+        }
+    }
+    if (gain == nullptr) return;
+    const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)width + eps);
+    for (int i = threadIdx.x; 2 * i < width; i += blockDim.x) {      // every thread rereads what it wrote itself
+        out[2 * i] = out[2 * i] * inv * gain[2 * i];
+        if (2 * i + 1 < width) out[2 * i + 1] = out[2 * i + 1] * inv * gain[2 * i + 1];
+    }
+}
+
+extern "C" int lb_embed_sinusoid(int dtype, const int32_t* tokens, const int32_t* positions, const void* table, const float* freq2, const float* gain,
+                                 float* x, int n_tokens, int width, float scale, float eps, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && width > 0 && freq2 != nullptr, "embed: bad sizes n_tokens=%d width=%d", n_tokens, width);
+    if (n_tokens == 0) return LB_OK;
+    const int threads = width >= 1024 ? 256 : 128;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (dtype == LB_F32) {
+        embed_sinusoid_kernel<float><<<n_tokens, threads, 0, s>>>(tokens, positions, (const float*)table, freq2, gain, x, width, scale, eps);
+    } else if (dtype == LB_BF16) {
+        embed_sinusoid_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(tokens, positions, (const __nv_bfloat16*)table, freq2, gain, x, width, scale, eps);
+    } else {
+        return lb_fail(LB_ERR_INVALID_ARGUMENT, "embed: unknown dtype %d", dtype);
+    }
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}
+
 // ---------------------------------------------------------------- LayerNorm
 
 // y = (x - mean) / sqrt(var + eps) * w + b with the population variance of the

@@ -98,11 +98,14 @@ __global__ void rms_sum_add_kernel(float* __restrict__ x, int64_t ldx, Branches 
 template <typename T>
 __global__ void qk_norm_store_kernel(const float* __restrict__ proj, int64_t ld, int q_off, int k_off, int v_off, const float* __restrict__ qw,
                                      const float* __restrict__ kw, T* __restrict__ q_out, int64_t ldq, T* __restrict__ cache,
-                                     const int32_t* __restrict__ slot_mapping, int H, int G, int D, int E, int P, int page_size, int norm, float eps) {
+                                     const int32_t* __restrict__ slot_mapping, int H, int G, int D, int E, int P, int page_size, int norm, float eps,
+                                     const int32_t* __restrict__ positions, float temp_coef, int temp_every) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const float* row = proj + (size_t)t * ld;
+    // The queries' temperature: 1 + coef ln(floor((pos + 1) / every) + 1), one factor a token.
+    const float temperature = temp_every > 0 ? fmaf(temp_coef, logf((float)((positions[t] + 1) / temp_every + 1)), 1.0f) : 1.0f;
     const int slot = cache != nullptr ? slot_mapping[t] : -1;
     const size_t plane = (size_t)G * page_size * P;
     for (int job = warp; job < H + 2 * G; job += n_warps) {
@@ -133,11 +136,13 @@ __global__ void qk_norm_store_kernel(const float* __restrict__ proj, int64_t ld,
             for (int d = lane; d < n; d += 32) ss = fmaf(src[d], src[d], ss);
             inv = 1.0f / sqrtf(lb_warp_sum(ss) / (float)n + eps);
         }
+        const float factor = job < H ? temperature : 1.0f;
         for (int d = lane; d < P; d += 32) {
             float v = 0.0f;
             if (d < n) {
                 v = src[d] * inv;
                 if (normed && gain != nullptr) v *= gain[d];
+                v *= factor;
             }
             dst[d] = lb_from_float<T>(v);
         }
@@ -177,7 +182,8 @@ __global__ void head_gate_kernel(const TI* __restrict__ o, int64_t ldo, int o_he
 
 // ---------------------------------------------------------------- mid[r, c] = act(gu[r, c]) * gu[r, F + c]
 template <typename TO>
-__global__ void gated_act_kernel(const float* __restrict__ gu, int64_t ld, TO* __restrict__ mid, int64_t ldm, int n_rows, int F, int act) {
+__global__ void gated_act_kernel(const float* __restrict__ gu, int64_t ld, TO* __restrict__ mid, int64_t ldm, int n_rows, int F, int act, float alpha,
+                                 float limit) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const long total = (long)n_rows * F;
@@ -185,8 +191,7 @@ __global__ void gated_act_kernel(const float* __restrict__ gu, int64_t ld, TO* _
         const long r = i / F;
         const int c = (int)(i - r * F);
         const float a = gu[(size_t)r * ld + c], u = gu[(size_t)r * ld + F + c];
-        const float z = act == 1 ? a * lb_sigmoid(a) : act == 2 ? lb_gelu_tanh(a) : lb_sigmoid(a);
-        mid[(size_t)r * ldm + c] = lb_from_float<TO>(z * u);
+        mid[(size_t)r * ldm + c] = lb_from_float<TO>(lb_gated_pair(a, u, act, alpha, limit));
     }
 }
 
@@ -221,6 +226,15 @@ extern "C" int lb_rms_sum_add(float* x, int64_t ldx, int n_branches, const float
 extern "C" int lb_qk_norm_store(int dtype, const float* proj, int64_t ld, int q_off, int k_off, int v_off, const float* q_weight, const float* k_weight,
                                 void* q_out, int64_t ldq, void* cache, const int32_t* slot_mapping, int n_tokens, int n_head, int n_kv_head, int dim,
                                 int vdim, int padded, int page_size, int norm, float eps, void* stream) {
+    return lb_qk_norm_store_tempered(dtype, proj, ld, q_off, k_off, v_off, q_weight, k_weight, q_out, ldq, cache, slot_mapping, n_tokens, n_head, n_kv_head,
+                                     dim, vdim, padded, page_size, norm, eps, nullptr, 0.0f, 0, stream);
+}
+
+extern "C" int lb_qk_norm_store_tempered(int dtype, const float* proj, int64_t ld, int q_off, int k_off, int v_off, const float* q_weight,
+                                         const float* k_weight, void* q_out, int64_t ldq, void* cache, const int32_t* slot_mapping, int n_tokens, int n_head,
+                                         int n_kv_head, int dim, int vdim, int padded, int page_size, int norm, float eps, const int32_t* positions,
+                                         float temp_coef, int temp_every, void* stream) {
+    LB_CHECK_ARG(temp_every >= 0 && (temp_every == 0 || positions != nullptr), "qk_norm_store: a temperature needs the tokens' positions");
     LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_kv_head > 0 && dim > 0 && vdim > 0 && padded >= dim && padded >= vdim && page_size > 0,
                  "qk_norm_store: bad sizes heads=%d/%d dim=%d vdim=%d padded=%d", n_head, n_kv_head, dim, vdim, padded);
     if (n_tokens == 0) return LB_OK;
@@ -228,11 +242,12 @@ extern "C" int lb_qk_norm_store(int dtype, const float* proj, int64_t ld, int q_
     const int jobs = n_head + 2 * n_kv_head, threads = 32 * min(8, jobs);
     if (dtype == LB_F32)
         LB_CHECK_CUDA(lb_launch_overlapped(qk_norm_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, proj, ld, q_off, k_off, v_off, q_weight, k_weight,
-                                           (float*)q_out, ldq, (float*)cache, slot_mapping, n_head, n_kv_head, dim, vdim, padded, page_size, norm, eps));
+                                           (float*)q_out, ldq, (float*)cache, slot_mapping, n_head, n_kv_head, dim, vdim, padded, page_size, norm, eps,
+                                           positions, temp_coef, temp_every));
     else if (dtype == LB_BF16)
         LB_CHECK_CUDA(lb_launch_overlapped(qk_norm_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, proj, ld, q_off, k_off, v_off, q_weight,
                                            k_weight, (__nv_bfloat16*)q_out, ldq, (__nv_bfloat16*)cache, slot_mapping, n_head, n_kv_head, dim, vdim, padded,
-                                           page_size, norm, eps));
+                                           page_size, norm, eps, positions, temp_coef, temp_every));
     else return lb_fail(LB_ERR_INVALID_ARGUMENT, "qk_norm_store: unknown dtype %d", dtype);
     return LB_OK;
 }
@@ -260,14 +275,19 @@ extern "C" int lb_head_gate(int in_dtype, int out_dtype, const void* o, int64_t 
 }
 
 extern "C" int lb_gated_act(int out_dtype, const float* gu, int64_t ld, void* mid, int64_t ldm, int n_rows, int inner, int act, void* stream) {
-    LB_CHECK_ARG(n_rows >= 0 && inner > 0 && act >= 0 && act <= 2, "gated_act: bad sizes");
+    return lb_gated_act_kind(out_dtype, gu, ld, mid, ldm, n_rows, inner, act, 0.0f, 0.0f, stream);
+}
+
+extern "C" int lb_gated_act_kind(int out_dtype, const float* gu, int64_t ld, void* mid, int64_t ldm, int n_rows, int inner, int act, float alpha, float limit,
+                                 void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && inner > 0 && act >= 0 && act <= LB_GATE_CAPPED, "gated_act: bad sizes");
     if (n_rows == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
     const dim3 grid(grid_for((long)n_rows * inner, 256)), block(256);
     if (out_dtype == LB_F32)
-        LB_CHECK_CUDA(lb_launch_overlapped(gated_act_kernel<float>, grid, block, 0, s, gu, ld, (float*)mid, ldm, n_rows, inner, act));
+        LB_CHECK_CUDA(lb_launch_overlapped(gated_act_kernel<float>, grid, block, 0, s, gu, ld, (float*)mid, ldm, n_rows, inner, act, alpha, limit));
     else if (out_dtype == LB_BF16)
-        LB_CHECK_CUDA(lb_launch_overlapped(gated_act_kernel<__nv_bfloat16>, grid, block, 0, s, gu, ld, (__nv_bfloat16*)mid, ldm, n_rows, inner, act));
+        LB_CHECK_CUDA(lb_launch_overlapped(gated_act_kernel<__nv_bfloat16>, grid, block, 0, s, gu, ld, (__nv_bfloat16*)mid, ldm, n_rows, inner, act, alpha, limit));
     else return lb_fail(LB_ERR_INVALID_ARGUMENT, "gated_act: unknown dtype %d", out_dtype);
     return LB_OK;
 }

@@ -1,14 +1,17 @@
 // Mixers whose memory is a matrix per head, carried from token to token:
 //     S_t = keep_t S_{t-1} + take_t k_t v_t^T,      o_t = S_t^T q_t (over a normaliser, where the mixer has one).
-// Two kinds of (keep, take):
+// Three kinds of (keep, take):
 //   fixed decay    keep = decay[h], take = 1, no normaliser (retention);
+//   token decay    keep = exp(f) with f <= 0 a number a token and head (the column zf holds f itself), take = 1, no normaliser:
+//                  the recurrence of a state space whose step depends on the input, its step folded into the values;
 //   gated          from two numbers a token and head, i (log of the input gate) and f (log of the forget gate), with a
 //                  running maximum m that starts at 0: m_t = max(f_t + m_{t-1}, i_t), keep = exp(f_t + m_{t-1} - m_t),
 //                  take = exp(i_t - m_t); a vector n_t follows the same recurrence with k alone, and
 //                  o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6).  The gates arrive as pre-activations:
 //                  i = cap tanh(zi / cap), f = logsigmoid(cap tanh(zf / cap)).
 // Queries and keys may be rotated first (the first rot_dims values of a head in pairs (j, j + rot_dims/2), angle =
-// position * freq[j]) and scaled.  State, gates, angles and every sum are 32-bit.
+// position * freq[j]) and scaled.  `qk_share` heads in a row may share one query and one key row (a group's).  State,
+// gates, angles and every sum are 32-bit.
 //
 // State of a request: [head][value tile][D x VT | D | 1] floats (S for the tile's VT value columns, n, m); every tile
 // keeps its own n and m, so that the blocks of a launch share nothing.
@@ -26,11 +29,11 @@
 namespace {
 
 struct MemoryArgs {
-    const float* q;            // [T, ld] rows, head h at columns h * D
+    const float* q;            // [T, ld] rows, head h at columns (h / qk_share) * D
     const float* k;
     const float* v;            // head h at columns h * E
     const float* zi;           // [T, ld] gate pre-activations, head h at column h (gated kind), else null
-    const float* zf;
+    const float* zf;           // the same; without zi and without decay: the log of keep itself (token decay)
     int64_t ld;
     const float* decay;        // [H] (fixed kind), else null
     const float* freq;         // [rot_dims / 2] or null
@@ -43,6 +46,7 @@ struct MemoryArgs {
     int64_t ldo;
     int H, D, E, VT, NV, rot_dims;
     float q_scale, k_scale, cap;
+    int qk_share;              // heads that read one query and key row; 1: every head its own
 };
 
 // Scratch of the three-launch form for long prompts, in which every piece of 32 rows is a block of its own.
@@ -95,6 +99,12 @@ __device__ __forceinline__ void gates(const MemoryArgs& a, int row, int h, float
         *m_new = 0.0f;
         return;
     }
+    if (a.zi == nullptr) {
+        *keep = expf(a.zf[(size_t)row * a.ld + h]);
+        *take = 1.0f;
+        *m_new = 0.0f;
+        return;
+    }
     const float gi = a.cap * tanhf(a.zi[(size_t)row * a.ld + h] / a.cap);
     const float gf = log_sigmoid(a.cap * tanhf(a.zf[(size_t)row * a.ld + h] / a.cap));
     const float m = fmaxf(gf + m_prev, gi);
@@ -126,11 +136,11 @@ __global__ void __launch_bounds__(256) matrix_memory_rows_kernel(MemoryArgs a, i
     float* raw = red + 256;                // [2][2 D + VT]: a row's queries, keys and values as they arrive, two rows in turn
     const int raw_row = 2 * D + VT;
     float* st = a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)D * VT + D + 1);
-    const bool gated = a.decay == nullptr;
+    const bool gated = a.zi != nullptr;
     auto ask = [&](int row, int buffer) {
         float* dst = raw + buffer * raw_row;
-        const float* q_row = a.q + (size_t)row * a.ld + (size_t)h * D;
-        const float* k_row = a.k + (size_t)row * a.ld + (size_t)h * D;
+        const float* q_row = a.q + (size_t)row * a.ld + (size_t)(h / a.qk_share) * D;
+        const float* k_row = a.k + (size_t)row * a.ld + (size_t)(h / a.qk_share) * D;
         const float* v_row = a.v + (size_t)row * a.ld + (size_t)h * E + nv * VT;
         for (int d = threadIdx.x; d < D; d += blockDim.x) {
             cp_async4(dst + d, q_row + d);
@@ -261,8 +271,8 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
     float* den = uj + kPiece;              // what divides row t
     float* sc = den + kPiece;              // [0] the old state's factor in the new one, [1] m_last
     int* pos_s = reinterpret_cast<int*>(sc + 2);      // the rows' positions
-    const bool gated = a.decay == nullptr;
-    const float logd = gated ? 0.0f : logf(a.decay[h]);       // -inf for a decay of 0: exp gives 0
+    const bool gated = a.zi != nullptr, token = a.decay == nullptr && !gated;
+    const float logd = a.decay == nullptr ? 0.0f : logf(a.decay[h]);       // -inf for a decay of 0: exp gives 0
     float* st = MODE == 0 ? a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)D * VT + D + 1)
                           : w.sums + (((size_t)blockIdx.x * a.H + h) * a.NV + nv) * ((size_t)D * VT + D);
     float m;
@@ -277,8 +287,8 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
         const int n = min(kPiece, row1 - p0);
         // The piece's rows as they are, all asked for at once (4-byte cp.async, one round trip), and the gates.
         for (int t = warp; t < n; t += kWarps) {          // a warp per row, lanes over the row's values
-            const float* q_row = a.q + (size_t)(p0 + t) * a.ld + (size_t)h * D;
-            const float* k_row = a.k + (size_t)(p0 + t) * a.ld + (size_t)h * D;
+            const float* q_row = a.q + (size_t)(p0 + t) * a.ld + (size_t)(h / a.qk_share) * D;
+            const float* k_row = a.k + (size_t)(p0 + t) * a.ld + (size_t)(h / a.qk_share) * D;
             for (int d = lane; d < D; d += 32) {
                 if (MODE != 1) cp_async4(qs + t * LDQ + d, q_row + d);       // a piece's own sum needs no queries
                 cp_async4(ks + t * LDQ + d, k_row + d);
@@ -298,17 +308,22 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
                 if (gated) {
                     i_log = a.cap * tanhf(a.zi[(size_t)row * a.ld + h] / a.cap);
                     f_log = log_sigmoid(a.cap * tanhf(a.zf[(size_t)row * a.ld + h] / a.cap));
+                } else if (token) {
+                    f_log = a.zf[(size_t)row * a.ld + h];
                 }
             }
-            if (gated) {
-                // b_t by a running sum over the lanes; m_t = b_t + max(m_prev, max_{j <= t} (i_j - b_j)), which is the recursion
-                // m_t = max(f_t + m_{t-1}, i_t) written out.
-                float b = f_log;
+            // b_t by a running sum over the lanes.
+            float b = f_log;
+            if (gated || token) {
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
                     const float up = __shfl_up_sync(0xffffffffu, b, o);
                     if (t >= o) b += up;
                 }
+                gb[t] = b;
+            }
+            if (gated) {
+                // m_t = b_t + max(m_prev, max_{j <= t} (i_j - b_j)), which is the recursion m_t = max(f_t + m_{t-1}, i_t) written out.
                 float best = i_log - b;
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
@@ -316,7 +331,6 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
                     if (t >= o) best = fmaxf(best, up);
                 }
                 gi[t] = i_log;
-                gb[t] = b;
                 gm[t] = b + fmaxf(m, best);
             }
         }
@@ -349,15 +363,18 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
             if (gated) {
                 al[t] = expf(gb[t] + m - gm[t]);
                 uj[t] = expf(gi[t] + gb[n - 1] - gb[t] - gm[n - 1]);
+            } else if (token) {
+                al[t] = expf(gb[t]);
+                uj[t] = t == n - 1 ? 1.0f : expf(gb[n - 1] - gb[t]);
             } else {
                 al[t] = expf((float)(t + 1) * logd);
                 uj[t] = t == n - 1 ? 1.0f : expf((float)(n - 1 - t) * logd);
             }
             if (t == 0) {
-                sc[0] = gated ? expf(gb[n - 1] + m - gm[n - 1]) : expf((float)n * logd);
+                sc[0] = gated ? expf(gb[n - 1] + m - gm[n - 1]) : token ? expf(gb[n - 1]) : expf((float)n * logd);
                 sc[1] = gated ? gm[n - 1] : 0.0f;
                 if (MODE == 1 && nv == 0) {
-                    w.scalars[((size_t)blockIdx.x * a.H + h) * 2] = gated ? gb[n - 1] : (float)n * logd;
+                    w.scalars[((size_t)blockIdx.x * a.H + h) * 2] = gated || token ? gb[n - 1] : (float)n * logd;
                     w.scalars[((size_t)blockIdx.x * a.H + h) * 2 + 1] = sc[1];
                 }
             }
@@ -379,7 +396,7 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
                     d3 = fmaf(q_row[d + 3], k_row[d + 3], d3);
                 }
                 for (; d < D; ++d) d0 = fmaf(q_row[d], k_row[d], d0);
-                const float w = gated ? expf(gi[j] + gb[t] - gb[j] - gm[t]) : (t == j ? 1.0f : expf((float)(t - j) * logd));
+                const float w = gated ? expf(gi[j] + gb[t] - gb[j] - gm[t]) : t == j ? 1.0f : token ? expf(gb[t] - gb[j]) : expf((float)(t - j) * logd);
                 p = ((d0 + d1) + (d2 + d3)) * w;
             }
             P[t * LDP + j] = p;
@@ -461,7 +478,7 @@ __global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryArgs a, P
     float* S = smem;                    // [count]
     float* buf = S + count;             // [2][count]
     float* st = a.state + (size_t)a.slots[seq] * a.slot_stride + ((size_t)h * a.NV + nv) * ((size_t)count + 1);
-    const bool gated = a.decay == nullptr;
+    const bool gated = a.zi != nullptr;
     auto sum_of = [&](int g) { return w.sums + (((size_t)g * a.H + h) * a.NV + nv) * (size_t)count; };
     for (int i = threadIdx.x; i < count; i += blockDim.x) {
         cp_async4(S + i, st + i);
@@ -512,17 +529,18 @@ struct PieceScratch {
 static int matrix_memory_run(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
                              const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
                              int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
-                             float k_scale, float cap, int chunked, const PieceScratch* pieces, void* stream) {
+                             float k_scale, float cap, int chunked, const PieceScratch* pieces, int qk_share, void* stream) {
     LB_CHECK_ARG(n_seq >= 0 && n_head > 0 && dim > 0 && vdim > 0 && value_tile > 0 && value_tile <= 64, "matrix memory: bad sizes heads=%d dim=%d vdim=%d tile=%d",
                  n_head, dim, vdim, value_tile);
-    LB_CHECK_ARG((decay != nullptr) != (zi != nullptr && zf != nullptr), "matrix memory: either a fixed decay or the two gates");
+    LB_CHECK_ARG(decay != nullptr ? (zi == nullptr && zf == nullptr) : zf != nullptr, "matrix memory: a fixed decay, or the two gates, or the log of a decay a token");
+    LB_CHECK_ARG(qk_share >= 1 && n_head % qk_share == 0, "matrix memory: %d heads do not share queries and keys in groups of %d", n_head, qk_share);
     LB_CHECK_ARG(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq != nullptr), "matrix memory: %d of %d values to rotate", rot_dims, dim);
     if (n_seq == 0) return LB_OK;
     MemoryArgs a{};
     a.q = q; a.k = k; a.v = v; a.zi = zi; a.zf = zf; a.ld = ld; a.decay = decay; a.freq = freq; a.positions = positions; a.q_start = q_start;
     a.slots = slots; a.state = state; a.slot_stride = slot_stride; a.out = out; a.ldo = ldo;
     a.H = n_head; a.D = dim; a.E = vdim; a.VT = value_tile; a.NV = (vdim + value_tile - 1) / value_tile; a.rot_dims = rot_dims;
-    a.q_scale = q_scale; a.k_scale = k_scale; a.cap = cap;
+    a.q_scale = q_scale; a.k_scale = k_scale; a.cap = cap; a.qk_share = qk_share;
     LB_CHECK_ARG(slot_stride >= (int64_t)n_head * a.NV * ((int64_t)dim * value_tile + dim + 1), "matrix memory: the state slots are too small");
     int p2 = 1;
     while (p2 < value_tile) p2 <<= 1;
@@ -564,7 +582,15 @@ extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, 
                                 int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
                                 float k_scale, float cap, int chunked, void* stream) {
     return matrix_memory_run(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim, vdim,
-                             value_tile, q_scale, k_scale, cap, chunked, nullptr, stream);
+                             value_tile, q_scale, k_scale, cap, chunked, nullptr, 1, stream);
+}
+
+extern "C" int lb_matrix_memory_shared(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                                       const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
+                                       int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
+                                       float k_scale, float cap, int chunked, int qk_share, void* stream) {
+    return matrix_memory_run(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim, vdim,
+                             value_tile, q_scale, k_scale, cap, chunked, nullptr, qk_share, stream);
 }
 
 extern "C" int64_t lb_matrix_memory_pieces_floats(int n_tokens, int n_seq, int n_head, int dim, int vdim, int value_tile) {
@@ -572,14 +598,22 @@ extern "C" int64_t lb_matrix_memory_pieces_floats(int n_tokens, int n_seq, int n
     return pieces * n_head * (tiles * ((int64_t)dim * value_tile + dim) + 3);
 }
 
-extern "C" int lb_matrix_memory_pieces(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
-                                       const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots,
-                                       float* state, int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq, int n_head, int dim, int vdim,
-                                       int value_tile, float q_scale, float k_scale, float cap, float* scratch, void* stream) {
+extern "C" int lb_matrix_memory_pieces_shared(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                                              const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots,
+                                              float* state, int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq, int n_head, int dim, int vdim,
+                                              int value_tile, float q_scale, float k_scale, float cap, float* scratch, int qk_share, void* stream) {
     LB_CHECK_ARG(scratch != nullptr && n_tokens >= 0 && value_tile > 0, "matrix memory in pieces: no scratch");
     const int64_t pieces = n_tokens / 32 + n_seq, tiles = (vdim + value_tile - 1) / value_tile;
     const int64_t sums = pieces * n_head * tiles * ((int64_t)dim * value_tile + dim);
     const PieceScratch ps{scratch, scratch + sums, scratch + sums + pieces * n_head * 2, (int)pieces};
     return matrix_memory_run(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim, vdim,
-                             value_tile, q_scale, k_scale, cap, 1, &ps, stream);
+                             value_tile, q_scale, k_scale, cap, 1, &ps, qk_share, stream);
+}
+
+extern "C" int lb_matrix_memory_pieces(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                                       const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots,
+                                       float* state, int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq, int n_head, int dim, int vdim,
+                                       int value_tile, float q_scale, float k_scale, float cap, float* scratch, void* stream) {
+    return lb_matrix_memory_pieces_shared(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_tokens, n_seq,
+                                          n_head, dim, vdim, value_tile, q_scale, k_scale, cap, scratch, 1, stream);
 }

@@ -21,7 +21,7 @@ __device__ __forceinline__ float lb_sigmoid(float z) { return 1.0f / (1.0f + exp
 // ---------------------------------------------------------------- router
 template <typename T>
 __global__ void router_topk_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ router, int32_t* __restrict__ ids,
-                                   float* __restrict__ weights, int E, int width, int top, int softmax, int renormalise) {
+                                   float* __restrict__ weights, int E, int width, int top, int softmax, int renormalise, const float* __restrict__ bias) {
     extern __shared__ float z[];       // [E]
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
@@ -44,7 +44,7 @@ __global__ void router_topk_kernel(const T* __restrict__ h, int64_t ldh, const T
             for (int u = 0; u < 8; ++u) acc = fmaf(a[u], b[u], acc);
         }
         acc = lb_warp_sum(acc);
-        if (lane == 0) z[e] = acc;
+        if (lane == 0) z[e] = bias != nullptr ? acc + bias[e] : acc;
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
@@ -129,10 +129,11 @@ struct ProductArgs {
     int64_t expert_stride;     // elements between two experts' matrices
     const int32_t* offsets;    // [E + 1]
     const int32_t* pair_at;    // [pairs]
-    const float* weights;      // [pairs]
+    const float* weights;      // [pairs], or null where the weight multiplies the experts' results instead (lb_expert_combine_weighted)
     void* out;                 // first half: mid [pairs, ldo] of the element type; second: y [pairs, ldo] float
     int64_t ldo;
     int E, N, K, top, act;
+    float alpha, limit;        // the capped gate's two numbers
 };
 
 constexpr int kBN = 64, kBK = 16;
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(256) expert_product_kernel(ProductArgs p) {
             if (GATED) {
                 const int pair = p.pair_at[r];
                 a_src[i] = A + (size_t)(pair / p.top) * p.lda;
-                a_scale[i] = p.weights[pair];
+                if (p.weights != nullptr) a_scale[i] = p.weights[pair];
             } else {
                 a_src[i] = A + (size_t)r * p.lda;
             }
@@ -239,9 +240,7 @@ __global__ void __launch_bounds__(256) expert_product_kernel(ProductArgs p) {
             const int n = n0 + tx * 4 + j;
             if (n >= p.N) continue;
             if (GATED) {
-                const float g = acc[i][j];
-                const float z = p.act == 1 ? g * lb_sigmoid(g) : p.act == 2 ? lb_gelu_tanh(g) : lb_sigmoid(g);
-                static_cast<T*>(p.out)[(size_t)r * p.ldo + n] = lb_from_float<T>(z * acc2[i][j]);
+                static_cast<T*>(p.out)[(size_t)r * p.ldo + n] = lb_from_float<T>(lb_gated_pair(acc[i][j], acc2[i][j], p.act, p.alpha, p.limit));
             } else {
                 static_cast<float*>(p.out)[(size_t)r * p.ldo + n] = acc[i][j];
             }
@@ -374,7 +373,7 @@ __global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) 
     }
     // The rows' weights (first half), then the gate.
     float w_lo = 1.0f, w_hi = 1.0f;
-    if (GATED) {
+    if (GATED && p.weights != nullptr) {
         const int lo = r0 + warp * 16 + g, hi = lo + 8;
         if (lo < r_end) w_lo = p.weights[p.pair_at[lo]];
         if (hi < r_end) w_hi = p.weights[p.pair_at[hi]];
@@ -387,9 +386,7 @@ __global__ void __launch_bounds__(128) expert_product_mma_kernel(ProductArgs p) 
             if (row >= r_end || n >= p.N) continue;
             if (GATED) {
                 const float w = e4 >= 2 ? w_hi : w_lo;
-                const float z = w * acc[nt][e4];
-                const float a = p.act == 1 ? z * lb_sigmoid(z) : p.act == 2 ? lb_gelu_tanh(z) : lb_sigmoid(z);
-                static_cast<B16*>(p.out)[(size_t)row * p.ldo + n] = __float2bfloat16_rn(a * (w * acc2[nt][e4]));
+                static_cast<B16*>(p.out)[(size_t)row * p.ldo + n] = __float2bfloat16_rn(lb_gated_pair(w * acc[nt][e4], w * acc2[nt][e4], p.act, p.alpha, p.limit));
             } else {
                 static_cast<float*>(p.out)[(size_t)row * p.ldo + n] = acc[nt][e4];
             }
@@ -409,7 +406,7 @@ bool mma_takes(const ProductArgs& p) {
 }
 
 __global__ void expert_combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ place,
-                                      int n_rows, int width, int top) {
+                                      int n_rows, int width, int top, const float* __restrict__ weights) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const long total = (long)n_rows * width;
@@ -417,7 +414,10 @@ __global__ void expert_combine_kernel(float* __restrict__ x, int64_t ldx, const 
         const long t = i / width;
         const int c = (int)(i - t * width);
         float acc = 0.0f;
-        for (int k = 0; k < top; ++k) acc += y[(size_t)place[t * top + k] * ldy + c];
+        if (weights != nullptr)
+            for (int k = 0; k < top; ++k) acc = fmaf(weights[t * top + k], y[(size_t)place[t * top + k] * ldy + c], acc);
+        else
+            for (int k = 0; k < top; ++k) acc += y[(size_t)place[t * top + k] * ldy + c];
         x[(size_t)t * ldx + c] += acc;
     }
 }
@@ -438,6 +438,11 @@ int launch_product(const ProductArgs& p, int n_pairs, cudaStream_t s) {
 
 extern "C" int lb_router_topk(int dtype, const void* h, int64_t ldh, const void* router, int32_t* ids, float* weights, int n_rows, int n_experts,
                               int width, int top, int softmax, int renormalise, void* stream) {
+    return lb_router_topk_biased(dtype, h, ldh, router, nullptr, ids, weights, n_rows, n_experts, width, top, softmax, renormalise, stream);
+}
+
+extern "C" int lb_router_topk_biased(int dtype, const void* h, int64_t ldh, const void* router, const float* bias, int32_t* ids, float* weights, int n_rows,
+                                     int n_experts, int width, int top, int softmax, int renormalise, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && n_experts > 0 && width > 0 && top > 0 && top <= n_experts && n_experts <= 4096, "router: top %d of %d experts", top, n_experts);
     if (n_rows == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
@@ -445,10 +450,10 @@ extern "C" int lb_router_topk(int dtype, const void* h, int64_t ldh, const void*
     const int threads = 32 * max(1, min(16, n_experts));       // a warp per expert, up to sixteen
     if (dtype == LB_F32)
         LB_CHECK_CUDA(lb_launch_overlapped(router_topk_kernel<float>, dim3(n_rows), dim3(threads), smem, s, (const float*)h, ldh, (const float*)router, ids, weights,
-                                           n_experts, width, top, softmax, renormalise));
+                                           n_experts, width, top, softmax, renormalise, bias));
     else if (dtype == LB_BF16)
         LB_CHECK_CUDA(lb_launch_overlapped(router_topk_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, s, (const __nv_bfloat16*)h, ldh,
-                                           (const __nv_bfloat16*)router, ids, weights, n_experts, width, top, softmax, renormalise));
+                                           (const __nv_bfloat16*)router, ids, weights, n_experts, width, top, softmax, renormalise, bias));
     else return lb_fail(LB_ERR_INVALID_ARGUMENT, "router: unknown dtype %d", dtype);
     return LB_OK;
 }
@@ -472,9 +477,16 @@ extern "C" int lb_expert_product_set_plain(int on) {
 extern "C" int lb_expert_product(int dtype, int gated, const void* a, int64_t lda, const void* w, int64_t expert_stride, const int32_t* offsets,
                                  const int32_t* pair_at, const float* weights, void* out, int64_t ldo, int n_pairs, int n_experts, int n, int k, int top,
                                  int act, void* stream) {
-    LB_CHECK_ARG(n_pairs >= 0 && n_experts > 0 && n > 0 && k > 0 && top > 0, "expert product: bad sizes");
+    return lb_expert_product_kind(dtype, gated, a, lda, w, expert_stride, offsets, pair_at, weights, out, ldo, n_pairs, n_experts, n, k, top, act, 0.0f, 0.0f,
+                                  stream);
+}
+
+extern "C" int lb_expert_product_kind(int dtype, int gated, const void* a, int64_t lda, const void* w, int64_t expert_stride, const int32_t* offsets,
+                                      const int32_t* pair_at, const float* weights, void* out, int64_t ldo, int n_pairs, int n_experts, int n, int k, int top,
+                                      int act, float alpha, float limit, void* stream) {
+    LB_CHECK_ARG(n_pairs >= 0 && n_experts > 0 && n > 0 && k > 0 && top > 0 && act >= 0 && act <= LB_GATE_CAPPED, "expert product: bad sizes");
     if (n_pairs == 0) return LB_OK;
-    ProductArgs p{a, lda, w, expert_stride, offsets, pair_at, weights, out, ldo, n_experts, n, k, top, act};
+    ProductArgs p{a, lda, w, expert_stride, offsets, pair_at, weights, out, ldo, n_experts, n, k, top, act, alpha, limit};
     auto s = static_cast<cudaStream_t>(stream);
     if (dtype == LB_F32) return gated ? launch_product<float, true>(p, n_pairs, s) : launch_product<float, false>(p, n_pairs, s);
     if (dtype == LB_BF16 && mma_takes(p) && !lb_expert_product_plain_only)
@@ -484,11 +496,16 @@ extern "C" int lb_expert_product(int dtype, int gated, const void* a, int64_t ld
 }
 
 extern "C" int lb_expert_combine(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, int n_rows, int width, int top, void* stream) {
+    return lb_expert_combine_weighted(x, ldx, y, ldy, place, nullptr, n_rows, width, top, stream);
+}
+
+extern "C" int lb_expert_combine_weighted(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, const float* weights, int n_rows,
+                                          int width, int top, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && width > 0 && top > 0, "expert combine: bad sizes");
     if (n_rows == 0) return LB_OK;
     const long total = (long)n_rows * width;
     const int blocks = (int)min((total + 255) / 256, (long)148 * 16);
     LB_CHECK_CUDA(lb_launch_overlapped(expert_combine_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ldx, y, ldy, place, n_rows, width,
-                                       top));
+                                       top, weights));
     return LB_OK;
 }

@@ -1,6 +1,7 @@
 #include "builtin_parts.h"
 #include "parallel_parts.h"
 #include "gated_parts.h"
+#include "state_parts.h"
 
 #include <mutex>
 
@@ -52,6 +53,12 @@ void register_builtin_parts() {
         feed_forwards().add("routed", {RoutedExperts::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
                                            return std::make_shared<RoutedExperts>(s, p);
                                        }});
+        positions().add("sinusoid", {SinusoidPosition::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
+                                         return std::make_shared<SinusoidPosition>(s, p);
+                                     }});
+        mixers().add("state_space", {StateSpaceMixer::parameters, [](const PartSpec& s, const Params& p, const Runtime&) {
+                                         return std::make_shared<StateSpaceMixer>(s, p);
+                                     }});
         arrangements().add("parallel", {[](const LayerSpec& l, const LayerParts& parts, const Runtime&) {
                                return std::make_shared<ParallelBlock>(l, parts);
                            }});

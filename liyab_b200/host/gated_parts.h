@@ -62,8 +62,12 @@ inline std::vector<float> rotation_frequencies(int dims, double base) {
 // and multiplied by a gain of `dim` values shared by the heads.  score = (q . k) * scale over the keys that the mask
 // lets through: `window` w (the w latest) or `chunk` c (the earlier keys of the query's own chunk of c positions, chunks
 // counted from position 0 of the sequence), softmax, values; the heads are multiplied by gate(g) (`gate`: sigmoid, silu
-// or none) before the output projection.  No rotation: positions act through the mask alone.  dim and vdim may differ:
-// the cache and the attention kernels work on heads of `padded` values, the rest zeros, so the existing kernels serve.
+// or none) before the output projection.  No rotation: positions act through the mask and, where the part has them, through
+// two more options.  `q_temp_every` e > 0 with `q_temp_coef` c: the queries of position p are multiplied by
+// 1 + c ln(floor((p + 1) / e) + 1) after their norm.  `distance_bias`: every head has two learned numbers (the parameter
+// `distance`: r1 for all heads, then r2) and the score of the key d positions back loses r1 ln(1 + r2 d).  With `qk_gain` false
+// the norm of queries and keys has no gain.  dim and vdim may differ: the cache and the attention kernels work on heads of
+// `padded` values, the rest zeros, so the existing kernels serve.
 
 class GatedAttention final : public Mixer {
 public:
@@ -84,15 +88,19 @@ public:
             throw invalid_model("gated_attention: a window ({}) or a chunk ({}), not both, and neither negative", shape.window, shape.chunk);
         qk_norm = s.options.get_bool("qk_norm", false);
         eps = static_cast<float>(s.options.get_number("eps", 1e-6));
+        temp_coef = static_cast<float>(s.options.get_number("q_temp_coef", 0.0));
+        temp_every = static_cast<int>(s.options.get_int("q_temp_every", 0));
+        if (temp_every < 0) throw invalid_model("gated_attention: q_temp_every {} is negative", temp_every);
         const std::string gate_name = s.options.get_string("gate", "none");
         gate = gate_name == "none" ? -1 : kernels::gate_from_name(gate_name);
         proj = Linear(p, "proj.", "gated_attention.proj");
         out = Linear(p, "out.", "gated_attention.out");
         if (const Tensor* b = p.find("qkv_bias")) bias.set(static_cast<const float*>(b->data), 0, qkv_cols(), proj.weight.dim(0));
-        if (qk_norm) {
+        if (qk_norm && s.options.get_bool("qk_gain", true)) {
             q_gain = f32_or_null(&p.at("q_norm.weight"));
             k_gain = f32_or_null(&p.at("k_norm.weight"));
         }
+        if (s.options.get_bool("distance_bias", false)) shape.distance = f32_or_null(&p.at("distance"));
     }
     static std::vector<ParamDecl> parameters(const PartSpec& s) {
         const int64_t hidden = need_int(s, "hidden"), H = need_int(s, "n_head"), G = s.options.get_int("n_kv_head", H), D = need_int(s, "dim");
@@ -101,10 +109,11 @@ public:
         std::vector<ParamDecl> out;
         Linear::declare(out, "proj.", H * D + G * D + G * E + (gated ? H * E : 0), hidden, false);
         if (s.options.get_bool("bias", false)) out.push_back({"qkv_bias", {H * D + G * D + G * E}, ParamKind::Vector});
-        if (s.options.get_bool("qk_norm", false)) {
+        if (s.options.get_bool("qk_norm", false) && s.options.get_bool("qk_gain", true)) {
             out.push_back({"q_norm.weight", {D}, ParamKind::Vector});
             out.push_back({"k_norm.weight", {D}, ParamKind::Vector});
         }
+        if (s.options.get_bool("distance_bias", false)) out.push_back({"distance", {2 * H}, ParamKind::Vector});
         Linear::declare(out, "out.", hidden, H * E, false);
         return out;
     }
@@ -138,7 +147,8 @@ public:
     int64_t hidden = 0;
     int H = 0, G = 0, D = 0, E = 0, gate = -1;
     bool qk_norm = false;
-    float eps = 1e-6f;
+    float eps = 1e-6f, temp_coef = 0.0f;
+    int temp_every = 0;
     Linear proj, out;
     const float* q_gain = nullptr;
     const float* k_gain = nullptr;
@@ -161,7 +171,8 @@ private:
         a.page_size = view->group->page_size;
         const Rows q = ws.get("gated_attention.q", T, static_cast<int64_t>(H) * P, dt);
         const kernels::QkvColumns cols{0, H * D, H * D + G * D, H, G, D, E, P, a.page_size};
-        kernels::qk_norm_store(s, pr, cols, q_gain, k_gain, q, unit.write ? cache : nullptr, view->slot_mapping, T, qk_norm, eps);
+        kernels::qk_norm_store(s, pr, cols, q_gain, k_gain, q, unit.write ? cache : nullptr, view->slot_mapping, T, qk_norm, eps, ctx.positions, temp_coef,
+                               temp_every);
         ctx.tap("attention.q", q);
         const Rows att = ws.get("gated_attention.att", T, static_cast<int64_t>(H) * P, dt);
         const int reach = shape.chunk > 0 ? shape.chunk : shape.window;
@@ -374,11 +385,14 @@ private:
 
 // ---- the gated feed-forward: down(gate(W_gate h) * (W_up h)) ------------------------------------------------------
 // One product makes [gate | up] in 32-bit, the gate's activation and the product of the halves are one pass, the second
-// product adds into the stream.  `activation`: silu, sigmoid or gelu_tanh.
+// product adds into the stream.  `activation`: silu, sigmoid, gelu_tanh, relu, or capped with its two numbers `gate_alpha` and
+// `gate_limit`: g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1).
 
 class GatedFeedForward final : public FeedForward {
 public:
-    GatedFeedForward(const PartSpec& s, const Params& p) : inner(need_int(s, "inner")), gate(kernels::gate_from_name(s.options.get_string("activation", "silu"))) {
+    GatedFeedForward(const PartSpec& s, const Params& p)
+        : inner(need_int(s, "inner")), gate(kernels::gate_from_name(s.options.get_string("activation", "silu"))),
+          alpha(static_cast<float>(s.options.get_number("gate_alpha", 1.0))), limit(static_cast<float>(s.options.get_number("gate_limit", 0.0))) {
         gate_up = Linear(p, "gate_up.", "gated.gate_up");
         down = Linear(p, "down.", "gated.down");
     }
@@ -395,18 +409,22 @@ public:
         const Rows gu = ctx.workspace->get("gated.gate_up", T, 2 * inner, DType::F32);
         gate_up.forward(ctx, h, gu, T);
         const Rows mid = ctx.workspace->get("gated.inner", T, inner, ctx.runtime.dtype);
-        kernels::gated_act(ctx.stream(), gu, mid, T, gate);
+        kernels::gated_act(ctx.stream(), gu, mid, T, gate, alpha, limit);
         down.forward(ctx, mid, x, T, kernels::kNone, &x);
     }
     int64_t inner;
     int gate;
+    float alpha, limit;
     Linear gate_up, down;
 };
 
 // ---- routed experts --------------------------------------------------------------------------------------------------
 // z = router h in 32-bit; score = sigmoid(z) (`score` "sigmoid") or the softmax over the experts ("softmax"); every row goes to
-// its `top` experts with the largest scores, weights = their scores (divided by their sum with `renormalise`).  The weight
-// multiplies the expert's input: x += sum_e expert_e(w_e h), expert = down(gate(W_gate a) * (W_up a)) without biases.  With
+// its `top` experts with the largest scores, weights = their scores (divided by their sum with `renormalise`; a softmax that is
+// renormalised is the softmax over the chosen experts' z alone).  With `router_bias` a learned number an expert is added to z
+// before the choice.  `weight_on` "input": the weight multiplies the expert's input, x += sum_e expert_e(w_e h); "output": its
+// result, x += sum_e w_e expert_e(h).  expert = down(gate(W_gate a) * (W_up a)) without biases, `activation` as the gated
+// feed-forward's (the capped form with `gate_alpha`, `gate_limit`).  With
 // `shared_inner` > 0 a gated feed-forward of that size runs for every row and is added.  The experts' matrices are stacked:
 // gate_up [experts x 2 inner, hidden] (per expert its gate rows, then its up rows) and down [experts x hidden, inner].
 
@@ -414,13 +432,17 @@ class RoutedExperts final : public FeedForward {
 public:
     RoutedExperts(const PartSpec& s, const Params& p)
         : hidden(need_int(s, "hidden")), inner(need_int(s, "inner")), experts(static_cast<int>(need_int(s, "experts"))), top(static_cast<int>(need_int(s, "top"))),
-          gate(kernels::gate_from_name(s.options.get_string("activation", "silu"))), renormalise(s.options.get_bool("renormalise", false)) {
+          gate(kernels::gate_from_name(s.options.get_string("activation", "silu"))), renormalise(s.options.get_bool("renormalise", false)),
+          alpha(static_cast<float>(s.options.get_number("gate_alpha", 1.0))), limit(static_cast<float>(s.options.get_number("gate_limit", 0.0))) {
         if (top > experts) throw invalid_model("routed: top {} of {} experts", top, experts);
         const std::string score = s.options.get_string("score", "sigmoid");
         if (score != "sigmoid" && score != "softmax") throw unsupported("routed: score '{}' is not supported; supported: sigmoid, softmax", score);
         softmax = score == "softmax";
-        if (s.options.get_string("weight_on", "input") != "input") throw unsupported("routed: the weight multiplies the expert's input; 'weight_on' knows 'input' only");
+        const std::string weight_on = s.options.get_string("weight_on", "input");
+        if (weight_on != "input" && weight_on != "output") throw unsupported("routed: weight_on '{}' is not supported; supported: input, output", weight_on);
+        weight_on_output = weight_on == "output";
         router = p.at("router.weight");
+        if (s.options.get_bool("router_bias", false)) router_bias = f32_or_null(&p.at("router.bias"));
         gate_up = p.at("experts.gate_up.weight");
         down = p.at("experts.down.weight");
         if (s.options.get_int("shared_inner", 0) > 0) shared = std::make_unique<GatedFeedForward>(shared_spec(s), p.sub("shared."));
@@ -431,9 +453,11 @@ public:
     }
     static std::vector<ParamDecl> parameters(const PartSpec& s) {
         const int64_t hidden = need_int(s, "hidden"), inner = need_int(s, "inner"), E = need_int(s, "experts");
-        std::vector<ParamDecl> out{{"router.weight", {E, hidden}, ParamKind::Matrix},
-                                   {"experts.gate_up.weight", {E * 2 * inner, hidden}, ParamKind::Matrix},
-                                   {"experts.down.weight", {E * hidden, inner}, ParamKind::Matrix}};
+        std::vector<ParamDecl> out{{"router.weight", {E, hidden}, ParamKind::Matrix}};
+        if (s.options.get_bool("router_bias", false)) out.push_back({"router.bias", {E}, ParamKind::Vector});
+        for (ParamDecl d : std::vector<ParamDecl>{{"experts.gate_up.weight", {E * 2 * inner, hidden}, ParamKind::Matrix},
+                                   {"experts.down.weight", {E * hidden, inner}, ParamKind::Matrix}})
+            out.push_back(std::move(d));
         if (s.options.get_int("shared_inner", 0) > 0)
             for (const auto& d : GatedFeedForward::parameters(shared_spec(s))) out.push_back({"shared." + d.name, d.shape, d.kind});
         return out;
@@ -449,21 +473,24 @@ public:
         int32_t* place = static_cast<int32_t*>(ws.get("routed.place", T, top, DType::I32).data);
         int32_t* pair_at = static_cast<int32_t*>(ws.get("routed.pair_at", T, top, DType::I32).data);
         int32_t* offsets = static_cast<int32_t*>(ws.flat("routed.offsets", experts + 1, DType::I32));
-        kernels::router_topk(s, h, router, ids, weights, T, top, softmax, renormalise);
+        kernels::router_topk(s, h, router, ids, weights, T, top, softmax, renormalise, router_bias);
         kernels::expert_plan(s, ids, pairs, experts, offsets, place, pair_at);
         Rows mid = ws.get("routed.inner", T, static_cast<int64_t>(top) * inner, ctx.runtime.dtype);
         mid = Rows{mid.data, mid.dtype, static_cast<int64_t>(pairs), inner, inner};
         Rows y = ws.get("routed.out", T, static_cast<int64_t>(top) * hidden, DType::F32);
         y = Rows{y.data, y.dtype, static_cast<int64_t>(pairs), hidden, hidden};
-        kernels::expert_product(s, true, h, gate_up, experts, offsets, pair_at, weights, mid, pairs, static_cast<int>(inner), static_cast<int>(hidden), top, gate);
+        kernels::expert_product(s, true, h, gate_up, experts, offsets, pair_at, weight_on_output ? nullptr : weights, mid, pairs, static_cast<int>(inner),
+                                static_cast<int>(hidden), top, gate, alpha, limit);
         kernels::expert_product(s, false, mid, down, experts, offsets, pair_at, weights, y, pairs, static_cast<int>(hidden), static_cast<int>(inner), top, gate);
-        kernels::expert_combine(s, x, y, place, T, top);
+        kernels::expert_combine(s, x, y, place, T, top, weight_on_output ? weights : nullptr);
         ctx.tap("routed", x);
         if (shared) shared->forward(ctx, h, x);
     }
     int64_t hidden, inner;
     int experts, top, gate;
-    bool renormalise, softmax = false;
+    bool renormalise, softmax = false, weight_on_output = false;
+    float alpha, limit;
+    const float* router_bias = nullptr;
     Tensor router, gate_up, down;
     std::unique_ptr<GatedFeedForward> shared;
 };

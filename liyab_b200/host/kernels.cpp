@@ -55,6 +55,13 @@ void embed_positions(cudaStream_t s, const int32_t* tokens, const int32_t* posit
                              x.f32(), n_tokens, width, scale, s), "embed_positions");
 }
 
+void embed_sinusoid(cudaStream_t s, const int32_t* tokens, const int32_t* positions, const Tensor& table, const float* freq2, const float* gain,
+                    const Rows& x, int n_tokens, float scale, float eps) {
+    if (x.dtype != DType::F32 || table.shape.size() != 2 || table.dim(1) != x.cols || x.stride != x.cols) throw invalid_argument("embed: the stream does not fit the table");
+    check(lb_embed_sinusoid(code(table.dtype, "table"), tokens, positions, table.data, freq2, gain, x.f32(), n_tokens, static_cast<int>(x.cols), scale, eps, s),
+          "embed_sinusoid");
+}
+
 void gather_tokens(cudaStream_t s, int32_t* dst, const int32_t* src, const int32_t* map, int n) {
     check(lb_gather_tokens(dst, src, map, n, s), "gather_tokens");
 }
@@ -228,9 +235,9 @@ void attention_generic(cudaStream_t s, DType dtype, const Rows& q, const void* c
                        const int32_t* positions, const int32_t* block_table, int table_width, const Rows& out, int n_tokens,
                        const AttentionShape& a) {
     if (q.dtype != dtype || out.dtype != dtype) throw invalid_argument("attention: q, cache and out must have one element type");
-    check(lb_paged_attention_generic(code(dtype, "cache"), q.data, q.stride, cache, tok_seq, positions, block_table, table_width,
+    check(lb_paged_attention_generic_biased(code(dtype, "cache"), q.data, q.stride, cache, tok_seq, positions, block_table, table_width,
                                      out.data, out.stride, n_tokens, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale,
-                                     a.mask(), s), "paged_attention_generic");
+                                     a.mask(), a.distance, s), "paged_attention_generic");
 }
 
 void decode_attention(cudaStream_t s, bool tensor_cores, const Rows& q, const void* cache, int n_pages, const int32_t* positions,
@@ -295,17 +302,20 @@ void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, cons
 }
 
 void qk_norm_store(cudaStream_t s, const Rows& proj, const QkvColumns& c, const float* q_weight, const float* k_weight, const Rows& q_out, void* cache,
-                   const int32_t* slot_mapping, int n_tokens, bool norm, float eps) {
+                   const int32_t* slot_mapping, int n_tokens, bool norm, float eps, const int32_t* positions, float temp_coef, int temp_every) {
     if (proj.dtype != DType::F32 || q_out.cols != static_cast<int64_t>(c.n_head) * c.padded) throw invalid_argument("qk_norm_store: buffers do not fit");
-    check(lb_qk_norm_store(code(q_out.dtype, "q_out"), proj.f32(), proj.stride, c.q_off, c.k_off, c.v_off, q_weight, k_weight, q_out.data, q_out.stride, cache,
-                           slot_mapping, n_tokens, c.n_head, c.n_kv_head, c.dim, c.vdim, c.padded, c.page_size, norm ? 1 : 0, eps, s), "qk_norm_store");
+    check(lb_qk_norm_store_tempered(code(q_out.dtype, "q_out"), proj.f32(), proj.stride, c.q_off, c.k_off, c.v_off, q_weight, k_weight, q_out.data, q_out.stride,
+                                    cache, slot_mapping, n_tokens, c.n_head, c.n_kv_head, c.dim, c.vdim, c.padded, c.page_size, norm ? 1 : 0, eps, positions,
+                                    temp_coef, temp_every, s), "qk_norm_store");
 }
 
 int gate_from_name(const std::string& name) {
     if (name == "sigmoid") return kSigmoid;
     if (name == "silu") return kSilu;
     if (name == "gelu_tanh") return kGeluGate;
-    throw unsupported("gate '{}' is not supported; supported: sigmoid, silu, gelu_tanh", name);
+    if (name == "relu") return kRelu;
+    if (name == "capped") return kCapped;
+    throw unsupported("gate '{}' is not supported; supported: sigmoid, silu, gelu_tanh, relu, capped", name);
 }
 
 void head_gate(cudaStream_t s, const Rows& o, int o_head, const Rows& g, const float* gain, const Rows& out, int n_tokens, int n_head, int vdim, bool norm,
@@ -315,9 +325,9 @@ void head_gate(cudaStream_t s, const Rows& o, int o_head, const Rows& g, const f
                        vdim, norm ? 1 : 0, gate, eps, s), "head_gate");
 }
 
-void gated_act(cudaStream_t s, const Rows& gu, const Rows& mid, int n_rows, int gate) {
+void gated_act(cudaStream_t s, const Rows& gu, const Rows& mid, int n_rows, int gate, float alpha, float limit) {
     if (gu.dtype != DType::F32 || gu.cols != 2 * mid.cols) throw invalid_argument("gated_act: buffers do not fit");
-    check(lb_gated_act(code(mid.dtype, "mid"), gu.f32(), gu.stride, mid.data, mid.stride, n_rows, static_cast<int>(mid.cols), gate, s), "gated_act");
+    check(lb_gated_act_kind(code(mid.dtype, "mid"), gu.f32(), gu.stride, mid.data, mid.stride, n_rows, static_cast<int>(mid.cols), gate, alpha, limit, s), "gated_act");
 }
 
 int memory_value_tile(int dim, int vdim) {
@@ -335,9 +345,9 @@ void matrix_memory(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, 
     if (q.dtype != DType::F32 || out.dtype != DType::F32 || k.stride != q.stride || v.stride != q.stride || (zi != nullptr && zi->stride != q.stride) ||
         (zf != nullptr && zf->stride != q.stride))
         throw invalid_argument("matrix memory: queries, keys, values and gates are column blocks of one float buffer");
-    check(lb_matrix_memory(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay, freq,
-                           m.rot_dims, positions, q_start, slots, state, m.slot_floats(), out.f32(), out.stride, n_seq, m.n_head, m.dim, m.vdim,
-                           m.value_tile, m.q_scale, m.k_scale, m.cap, chunked ? 1 : 0, s), "matrix_memory");
+    check(lb_matrix_memory_shared(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay, freq,
+                                  m.rot_dims, positions, q_start, slots, state, m.stride(), out.f32(), out.stride, n_seq, m.n_head, m.dim, m.vdim,
+                                  m.value_tile, m.q_scale, m.k_scale, m.cap, chunked ? 1 : 0, m.qk_share, s), "matrix_memory");
 }
 
 int64_t memory_pieces_floats(int n_tokens, int n_seq, const MemoryShape& m) {
@@ -350,16 +360,17 @@ void matrix_memory_pieces(cudaStream_t s, const Rows& q, const Rows& k, const Ro
     if (q.dtype != DType::F32 || out.dtype != DType::F32 || k.stride != q.stride || v.stride != q.stride || (zi != nullptr && zi->stride != q.stride) ||
         (zf != nullptr && zf->stride != q.stride))
         throw invalid_argument("matrix memory: queries, keys, values and gates are column blocks of one float buffer");
-    check(lb_matrix_memory_pieces(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay, freq,
-                                  m.rot_dims, positions, q_start, slots, state, m.slot_floats(), out.f32(), out.stride, n_tokens, n_seq, m.n_head, m.dim,
-                                  m.vdim, m.value_tile, m.q_scale, m.k_scale, m.cap, scratch, s), "matrix_memory_pieces");
+    check(lb_matrix_memory_pieces_shared(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay,
+                                         freq, m.rot_dims, positions, q_start, slots, state, m.stride(), out.f32(), out.stride, n_tokens, n_seq, m.n_head,
+                                         m.dim, m.vdim, m.value_tile, m.q_scale, m.k_scale, m.cap, scratch, m.qk_share, s), "matrix_memory_pieces");
     launches.fetch_add(2, std::memory_order_relaxed);
 }
 
-void router_topk(cudaStream_t s, const Rows& h, const Tensor& router, int32_t* ids, float* weights, int n_rows, int top, bool softmax, bool renormalise) {
+void router_topk(cudaStream_t s, const Rows& h, const Tensor& router, int32_t* ids, float* weights, int n_rows, int top, bool softmax, bool renormalise,
+                 const float* bias) {
     if (router.shape.size() != 2 || router.dim(1) != h.cols || router.dtype != h.dtype) throw invalid_argument("router: the matrix does not fit the rows");
-    check(lb_router_topk(code(h.dtype, "h"), h.data, h.stride, router.data, ids, weights, n_rows, static_cast<int>(router.dim(0)), static_cast<int>(h.cols), top,
-                         softmax ? 1 : 0, renormalise ? 1 : 0, s), "router_topk");
+    check(lb_router_topk_biased(code(h.dtype, "h"), h.data, h.stride, router.data, bias, ids, weights, n_rows, static_cast<int>(router.dim(0)),
+                                static_cast<int>(h.cols), top, softmax ? 1 : 0, renormalise ? 1 : 0, s), "router_topk");
 }
 
 void expert_plan(cudaStream_t s, const int32_t* ids, int n_pairs, int n_experts, int32_t* offsets, int32_t* place, int32_t* pair_at) {
@@ -367,17 +378,38 @@ void expert_plan(cudaStream_t s, const int32_t* ids, int n_pairs, int n_experts,
 }
 
 void expert_product(cudaStream_t s, bool gated, const Rows& a, const Tensor& w, int n_experts, const int32_t* offsets, const int32_t* pair_at,
-                    const float* weights, const Rows& out, int n_pairs, int n, int k, int top, int gate) {
+                    const float* weights, const Rows& out, int n_pairs, int n, int k, int top, int gate, float alpha, float limit) {
     if (a.dtype != w.dtype || w.numel() != static_cast<int64_t>(n_experts) * (gated ? 2 : 1) * n * k || a.cols != k || out.cols != n)
         throw invalid_argument("expert product: shapes do not fit");
     if (out.dtype != (gated ? a.dtype : DType::F32)) throw invalid_argument("expert product: the output has the wrong type");
-    check(lb_expert_product(code(a.dtype, "a"), gated ? 1 : 0, a.data, a.stride, w.data, static_cast<int64_t>(gated ? 2 : 1) * n * k, offsets, pair_at, weights,
-                            out.data, out.stride, n_pairs, n_experts, n, k, top, gate, s), "expert_product");
+    check(lb_expert_product_kind(code(a.dtype, "a"), gated ? 1 : 0, a.data, a.stride, w.data, static_cast<int64_t>(gated ? 2 : 1) * n * k, offsets, pair_at,
+                                 weights, out.data, out.stride, n_pairs, n_experts, n, k, top, gate, alpha, limit, s), "expert_product");
 }
 
-void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top) {
+void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top, const float* weights) {
     if (x.dtype != DType::F32 || y.dtype != DType::F32 || x.cols != y.cols) throw invalid_argument("expert combine: buffers do not fit");
-    check(lb_expert_combine(x.f32(), x.stride, y.f32(), y.stride, place, n_rows, static_cast<int>(x.cols), top, s), "expert_combine");
+    check(lb_expert_combine_weighted(x.f32(), x.stride, y.f32(), y.stride, place, weights, n_rows, static_cast<int>(x.cols), top, s), "expert_combine");
+}
+
+void ssm_prepare(cudaStream_t s, const Rows& proj, const float* taps, const float* tap_bias, const float* dt_bias, const float* a_log, float* conv_state,
+                 int64_t slot_stride, const int32_t* tok_seq, const int32_t* q_start, const int32_t* slots, const Rows& out, int n_tokens, int n_seq,
+                 const StateSpaceShape& m, bool decode_only) {
+    if (proj.dtype != DType::F32 || out.dtype != DType::F32 || proj.cols != m.inner() + m.channels() + m.n_head || out.cols != m.prepared_cols())
+        throw invalid_argument("state space: the projection's or the prepared rows do not fit the shape");
+    check(lb_ssm_prepare(proj.f32(), proj.stride, static_cast<int>(m.inner()), static_cast<int>(m.inner() + m.channels()), taps, tap_bias, dt_bias, a_log,
+                         conv_state, slot_stride, tok_seq, q_start, slots, out.f32(), out.stride, n_tokens, n_seq, m.n_head, m.vdim,
+                         static_cast<int>(m.group_values()), m.taps, decode_only ? 1 : 0, s), "ssm_prepare");
+    if (!decode_only && m.taps > 1) launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+void gated_group_norm(cudaStream_t s, const Rows& o, const Rows* skip, const float* skip_gain, int head, const Rows* z, const float* weight, const Rows& out,
+                      int n_rows, int groups, float eps) {
+    if (o.dtype != DType::F32 || out.cols != o.cols || (skip != nullptr && (skip->dtype != DType::F32 || skip->cols != o.cols)) ||
+        (z != nullptr && (z->dtype != DType::F32 || z->cols != o.cols)))
+        throw invalid_argument("gated group norm: buffers do not fit");
+    check(lb_gated_group_norm(code(out.dtype, "out"), o.f32(), o.stride, skip != nullptr ? skip->f32() : nullptr, skip != nullptr ? skip->stride : 0, skip_gain,
+                              head, z != nullptr ? z->f32() : nullptr, z != nullptr ? z->stride : 0, weight, out.data, out.stride, n_rows,
+                              static_cast<int>(o.cols), groups, eps, s), "gated_group_norm");
 }
 
 void token_shift(cudaStream_t s, const Rows& h, const float* mix, const Rows& m, void* state, const ShiftLayout& l) {

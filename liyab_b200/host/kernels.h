@@ -36,6 +36,10 @@ struct KvDestination {
 
 void embed_positions(cudaStream_t s, const int32_t* tokens, const int32_t* positions, const Tensor& table,
                      const Tensor* pos_table, const Rows& x, int n_tokens, float scale);
+// x[t] = table[token t] * scale + the sinusoid of the token's position (entry 2i sin(p w_i), entry 2i + 1 cos(p w_i); freq2 holds every w_i
+// as two floats, leading part and rest); with `gain` [width] the row is then divided by its root mean square and multiplied by it.
+void embed_sinusoid(cudaStream_t s, const int32_t* tokens, const int32_t* positions, const Tensor& table, const float* freq2, const float* gain,
+                    const Rows& x, int n_tokens, float scale, float eps);
 void gather_tokens(cudaStream_t s, int32_t* dst, const int32_t* src, const int32_t* map, int n);
 void layernorm(cudaStream_t s, const Rows& x, const int32_t* rows, const float* weight, const float* bias, const Rows& out,
                int n_rows, float eps);
@@ -85,6 +89,8 @@ struct AttentionShape {
     float scale = 1.0f;
     int window = 0;          // w > 0: a query sees the w latest keys
     int chunk = 0;           // c > 0: a query sees the earlier keys of its own chunk of c positions, counted from position 0
+    // A penalty by distance: device floats r1 [n_head] then r2 [n_head]; the score of the key d positions back loses r1 ln(1 + r2 d).
+    const float* distance = nullptr;
     // One number for the kernels: 0 all earlier keys, w > 0 a window, -c a chunk (a shape has one of the two at most).
     int mask() const { return chunk > 0 ? -chunk : window; }
 };
@@ -171,27 +177,34 @@ void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, cons
 struct QkvColumns {
     int q_off = 0, k_off = 0, v_off = 0, n_head = 0, n_kv_head = 0, dim = 0, vdim = 0, padded = 0, page_size = 0;
 };
+// With temp_every > 0 the queries of the token at position p are multiplied by 1 + temp_coef ln(floor((p + 1) / temp_every) + 1).
 void qk_norm_store(cudaStream_t s, const Rows& proj, const QkvColumns& c, const float* q_weight, const float* k_weight, const Rows& q_out, void* cache,
-                   const int32_t* slot_mapping, int n_tokens, bool norm, float eps);
-enum Gate : int { kSigmoid = 0, kSilu = 1, kGeluGate = 2 };
+                   const int32_t* slot_mapping, int n_tokens, bool norm, float eps, const int32_t* positions = nullptr, float temp_coef = 0.0f,
+                   int temp_every = 0);
+// kCapped has two numbers (alpha, limit): g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1).
+enum Gate : int { kSigmoid = 0, kSilu = 1, kGeluGate = 2, kRelu = 3, kCapped = 4 };
 int gate_from_name(const std::string& name);
 // out[t, h * vdim + c] = f(o[t, h * o_head + c]) * gain * gate(g[t, h * vdim + c]); f: over the head's root mean square when `norm`;
 // rows g without data: no gate.
 void head_gate(cudaStream_t s, const Rows& o, int o_head, const Rows& g, const float* gain, const Rows& out, int n_tokens, int n_head, int vdim, bool norm,
                int gate, float eps);
 // mid[r, c] = gate(gu[r, c]) * gu[r, inner + c]; gu float [rows, 2 * inner].
-void gated_act(cudaStream_t s, const Rows& gu, const Rows& mid, int n_rows, int gate);
+void gated_act(cudaStream_t s, const Rows& gu, const Rows& mid, int n_rows, int gate, float alpha = 0.0f, float limit = 0.0f);
 
 // ---- a matrix memory per head, carried from token to token (retention with a fixed decay; gated with a running maximum) ----
 struct MemoryShape {
     int n_head = 0, dim = 0, vdim = 0, value_tile = 0, rot_dims = 0;
     float q_scale = 1.0f, k_scale = 1.0f, cap = 0.0f;
+    int qk_share = 1;                // heads that read one query and key row (a group's); 1: every head its own
+    int64_t slot_stride = 0;         // floats between two requests' states; 0: slot_floats() (a mixer may keep more in its slot)
+    int64_t stride() const { return slot_stride > 0 ? slot_stride : slot_floats(); }
     int tiles() const { return (vdim + value_tile - 1) / value_tile; }
     int64_t slot_floats() const { return static_cast<int64_t>(n_head) * tiles() * (static_cast<int64_t>(dim) * value_tile + dim + 1); }
 };
 // The value tile a shape gets (the state's layout depends on it, so it is chosen once per part).
 int memory_value_tile(int dim, int vdim);
-// q, k, v, zi, zf: column blocks of one float buffer (same stride); decay [n_head] or the two gates.
+// q, k, v, zi, zf: column blocks of one float buffer (same stride); decay [n_head], or the two gates, or zf alone: the log of keep itself,
+// a number a token and head (take = 1, no normaliser).
 void matrix_memory(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, const Rows* zi, const Rows* zf, const float* decay, const float* freq,
                    const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state, const Rows& out, int n_seq, const MemoryShape& m,
                    bool chunked);
@@ -202,11 +215,30 @@ void matrix_memory_pieces(cudaStream_t s, const Rows& q, const Rows& k, const Ro
                           const MemoryShape& m, float* scratch);
 
 // ---- routed experts ----
-void router_topk(cudaStream_t s, const Rows& h, const Tensor& router, int32_t* ids, float* weights, int n_rows, int top, bool softmax, bool renormalise);
+void router_topk(cudaStream_t s, const Rows& h, const Tensor& router, int32_t* ids, float* weights, int n_rows, int top, bool softmax, bool renormalise,
+                 const float* bias = nullptr);
 void expert_plan(cudaStream_t s, const int32_t* ids, int n_pairs, int n_experts, int32_t* offsets, int32_t* place, int32_t* pair_at);
 void expert_product(cudaStream_t s, bool gated, const Rows& a, const Tensor& w, int n_experts, const int32_t* offsets, const int32_t* pair_at,
-                    const float* weights, const Rows& out, int n_pairs, int n, int k, int top, int gate);
-void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top);
+                    const float* weights, const Rows& out, int n_pairs, int n, int k, int top, int gate, float alpha = 0.0f, float limit = 0.0f);
+// With `weights` [rows, top] every result is multiplied by its weight as it is added.
+void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top, const float* weights = nullptr);
+
+// ---- the pieces around a state space per head whose step depends on the input (the recurrence is the matrix memory's) ----
+struct StateSpaceShape {
+    int n_head = 0, vdim = 0, n_state = 0, groups = 0, taps = 0;
+    int64_t inner() const { return static_cast<int64_t>(n_head) * vdim; }
+    int64_t group_values() const { return 2 * static_cast<int64_t>(groups) * n_state; }
+    int64_t channels() const { return inner() + group_values(); }
+    int64_t conv_floats() const { return static_cast<int64_t>(taps - 1) * channels(); }
+    int64_t prepared_cols() const { return 2 * inner() + group_values() + n_head; }
+};
+// proj: float rows [z | x B C | dt]; out: float rows [x | B | C | dt x | log keep]; conv_state: the slots' [taps - 1][channels] floats.
+void ssm_prepare(cudaStream_t s, const Rows& proj, const float* taps, const float* tap_bias, const float* dt_bias, const float* a_log, float* conv_state,
+                 int64_t slot_stride, const int32_t* tok_seq, const int32_t* q_start, const int32_t* slots, const Rows& out, int n_tokens, int n_seq,
+                 const StateSpaceShape& m, bool decode_only);
+// out = (o + skip_gain[head] * skip) * silu(z) in `groups` equal parts, each over its root mean square, times weight.
+void gated_group_norm(cudaStream_t s, const Rows& o, const Rows* skip, const float* skip_gain, int head, const Rows* z, const float* weight, const Rows& out,
+                      int n_rows, int groups, float eps);
 
 void sample(cudaStream_t s, const float* logits, int64_t row_stride, int n_rows, int vocab, const float* temperature,
             const int32_t* top_k, const float* top_p, const double* uniform, int32_t* out_ids);

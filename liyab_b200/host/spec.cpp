@@ -150,6 +150,7 @@ Json CheckpointTensor::to_json() const {
     j.set("transform", transform);
     if (sources.size() > 1) j.set("concat_axis", concat_axis);
     if (slice_axis >= 0) j.set("slice", Json::object().set("axis", slice_axis).set("begin", slice_begin).set("end", slice_end));
+    if (repeat > 0) j.set("repeat", repeat);
     j.set("kind", param_kind_name(kind));
     j.set("init", Json::array().push(init_mean).push(init_std));
     return j;
@@ -167,6 +168,8 @@ CheckpointTensor CheckpointTensor::from_json(const Json& j, const std::string& w
             t.slice_begin = s->at("begin").as_int();
             t.slice_end = s->at("end").as_int();
         }
+        t.repeat = j.get_int("repeat", 0);
+        if (t.repeat < 0) throw invalid_model("{} repeats its number {} times", what, t.repeat);
         t.kind = param_kind_from_name(j.get_string("kind", "matrix"));
         if (const Json* init = j.find("init")) {
             t.init_mean = init->items().at(0).as_number();

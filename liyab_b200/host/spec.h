@@ -122,8 +122,10 @@ struct ParamDecl {
 // "transpose", for matrices stored [in, out]) is applied to every source; several
 // sources are joined along `concat_axis` (separate q, k, v matrices becoming one
 // fused projection); then, when `slice_axis` >= 0, rows [slice_begin, slice_end)
-// of that axis are kept (one half of a fused [gate | up]).  `init` is (mean, std)
-// for the random-weights mode.
+// of that axis are kept (one half of a fused [gate | up]).  With `repeat` > 0 the
+// result, which must then be a single number, is written `repeat` times and becomes a
+// vector of that length (a gain stored as one number for all coordinates).  `init` is
+// (mean, std) for the random-weights mode.
 struct CheckpointSource {
     std::string name;
     std::vector<int64_t> shape;
@@ -134,6 +136,7 @@ struct CheckpointTensor {
     int concat_axis = 0;
     int slice_axis = -1;
     int64_t slice_begin = 0, slice_end = 0;
+    int64_t repeat = 0;
     ParamKind kind = ParamKind::Matrix;
     double init_mean = 0.0, init_std = 0.02;
 
@@ -145,6 +148,12 @@ struct CheckpointTensor {
         t.transform = std::move(transform);
         t.init_mean = mean;
         t.init_std = std;
+        return t;
+    }
+    // A parameter of `count` equal entries from a file tensor that holds one number (shape []).
+    static CheckpointTensor repeated(std::string name, int64_t count, ParamKind kind = ParamKind::Vector, double mean = 0.0, double std = 0.02) {
+        CheckpointTensor t = one(std::move(name), {}, kind, "none", mean, std);
+        t.repeat = count;
         return t;
     }
     Json to_json() const;

@@ -2,45 +2,9 @@
 
 #include <cmath>
 
+#include "config_keys.h"
+
 namespace liyab {
-namespace {
-
-int64_t int_in(const Json& obj, const char* key, const std::string& where, int64_t lo, int64_t hi = int64_t{1} << 30) {
-    const Json* v = obj.find(key);
-    if (v == nullptr || !v->is_int() || v->as_int() < lo || v->as_int() > hi)
-        throw invalid_model("missing or invalid {}{} in config.json (got {}, need an integer in [{}, {}])", where, key, v == nullptr ? "nothing" : v->dump(), lo, hi);
-    return v->as_int();
-}
-
-double number_in(const Json& obj, const char* key, const std::string& where) {
-    const Json* v = obj.find(key);
-    if (v == nullptr || !v->is_number() || !std::isfinite(v->as_number()))
-        throw invalid_model("missing or invalid {}{} in config.json (got {}, need a finite number)", where, key, v == nullptr ? "nothing" : v->dump());
-    return v->as_number();
-}
-
-const Json& object_in(const Json& obj, const char* key, const std::string& where) {
-    const Json* v = obj.find(key);
-    if (v == nullptr || !v->is_object()) throw invalid_model("missing or invalid {}{} in config.json (need an object)", where, key);
-    return *v;
-}
-
-const Json* optional_in(const Json& obj, const char* key) {
-    const Json* v = obj.find(key);
-    return v == nullptr || v->is_null() ? nullptr : v;
-}
-
-CheckpointTensor joined(std::vector<CheckpointSource> sources, ParamKind kind, double std_dev = 0.02, double mean = 0.0) {
-    CheckpointTensor t;
-    t.sources = std::move(sources);
-    t.concat_axis = 0;
-    t.kind = kind;
-    t.init_mean = mean;
-    t.init_std = std_dev;
-    return t;
-}
-
-}  // namespace
 
 std::unique_ptr<VosuraxConfig> VosuraxConfig::parse(const Json& raw) {
     auto c = std::make_unique<VosuraxConfig>();

@@ -194,6 +194,14 @@ HostTensor assemble(ModelFiles& files, const std::string& prefix, const Checkpoi
         out.bytes = std::move(cut);
         out.shape[ax] = keep;
     }
+    if (spec.repeat > 0) {
+        if (shape_numel(out.shape) != 1) throw invalid_model("tensor '{}' of shape {} cannot be repeated: it is not a single number", spec.sources[0].name, shape_text(out.shape));
+        const size_t es = dtype_size(out.dtype);
+        std::vector<uint8_t> all(static_cast<size_t>(spec.repeat) * es);
+        for (int64_t i = 0; i < spec.repeat; ++i) std::memcpy(all.data() + static_cast<size_t>(i) * es, out.bytes.data(), es);
+        out.bytes = std::move(all);
+        out.shape = {spec.repeat};
+    }
     return out;
 }
 
