@@ -130,6 +130,12 @@ int lb_decode_attention(const void* q, int64_t q_stride, const void* cache, cons
                         int* counters, int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale,
                         int window, int n_splits, void* stream);
 int lb_decode_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size);
+/* lb_decode_attention with a penalty by distance: `distance` holds r1 [n_head] then r2 [n_head], and the score of the key d
+ * positions back loses r1 ln(1 + r2 d); null: none. */
+int lb_decode_attention_biased(const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
+                               int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
+                               int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits, const float* distance,
+                               void* stream);
 /* The same with scores and weighted values on the tensor cores (head_dim 64 or 128, up to 16 query heads per
  * key/value head, pages of 16 positions or more); same arguments, scratch and split semantics. */
 int lb_decode_attention_mma(const void* q, int64_t q_stride, const void* cache, int n_pages, const int32_t* positions,
@@ -150,6 +156,16 @@ int lb_prefill_attention(const void* q, int64_t q_stride, const void* cache, con
                          int64_t out_stride, int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim,
                          int page_size, float scale, int window, void* stream);
 int lb_prefill_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size);
+/* lb_prefill_attention and lb_prefill_attention_tc with a penalty by distance (`distance` as for lb_decode_attention_biased; the tcgen05
+ * kernel applies it to the raw scores and so needs scale != 0). */
+int lb_prefill_attention_biased(const void* q, int64_t q_stride, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len,
+                                int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance,
+                                void* stream);
+int lb_prefill_attention_tc_biased(const void* q, int64_t q_stride, int n_tokens, const void* cache, int n_pages, const int32_t* q_start,
+                                   const int32_t* n_past, const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
+                                   int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window,
+                                   const float* distance, void* stream);
 /* The same on the tcgen05 tensor cores (head size 64, pages of 16 positions or more): TMA-fed, scores and output
  * accumulated in tensor memory.  n_tokens is the number of rows of q (and out), n_pages the number of pages of the
  * layer's cache (both bound the tensor maps). */

@@ -58,7 +58,8 @@ __global__ void __launch_bounds__(kThreads)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache,
                         const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride,
                         __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ partial,
-                        int* __restrict__ counters, int n_kv_head, int page_shift, float scale, int window, int n_splits) {
+                        int* __restrict__ counters, int n_kv_head, int page_shift, float scale, int window, int n_splits,
+                        const float* __restrict__ distance) {
     constexpr int TPK = HD / 8;                 // threads that share a key
     constexpr int KPW = 32 / TPK;               // keys a warp covers with one load
     constexpr int STATE = HD + 2;               // m, l, values
@@ -87,6 +88,13 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
         unpack8(v, qf[g]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) qf[g][i] *= scale * kLog2e;
+    }
+    // The heads' pairs (r1, r2) of the penalty by distance; in the scores' base-2 scale a key d positions back loses r1 log2(1 + r2 d).
+    float r1[G], r2[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        r1[g] = distance != nullptr ? distance[kvh * G + g] : 0.0f;
+        r2[g] = distance != nullptr ? distance[n_kv_head * G + kvh * G + g] : 0.0f;
     }
     float m[G], l[G], acc[G][8];
 #pragma unroll
@@ -132,6 +140,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
 #pragma unroll
                 for (int o = TPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                 if (live) {
+                    if (distance != nullptr) s = fmaf(-r1[g], __log2f(fmaf(r2[g], (float)(pos - j), 1.0f)), s);
                     const float m_new = fmaxf(m[g], s);
                     const float corr = exp2f(m[g] - m_new);
                     const float p = exp2f(s - m_new);
@@ -227,11 +236,11 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
 template <int HD, int G>
 int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
            int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_kv_head,
-           int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
+           int page_shift, float scale, int window, int n_splits, const float* distance, cudaStream_t s) {
     dim3 grid(n_splits, n_kv_head, n_seq);
     LB_CHECK_CUDA(lb_launch_overlapped(decode_attention_kernel<HD, G>, dim3(grid), dim3(kThreads), 0, s, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
-        (__nv_bfloat16*)out, out_stride, partial, counters, n_kv_head, page_shift, scale, window, n_splits));
+        (__nv_bfloat16*)out, out_stride, partial, counters, n_kv_head, page_shift, scale, window, n_splits, distance));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
@@ -239,10 +248,10 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* po
 template <int HD>
 int by_group(int group, const void* q, int64_t q_stride, const void* cache, const int32_t* positions,
              const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial, int* counters,
-             int n_seq, int n_kv_head, int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
+             int n_seq, int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, cudaStream_t s) {
 #define LB_GO(G)                                                                                                   \
     return launch<HD, G>(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, \
-                         n_seq, n_kv_head, page_shift, scale, window, n_splits, s)
+                         n_seq, n_kv_head, page_shift, scale, window, n_splits, distance, s)
     switch (group) {
         case 1: LB_GO(1);
         case 2: LB_GO(2);
@@ -273,6 +282,14 @@ extern "C" int lb_decode_attention(const void* q, int64_t q_stride, const void* 
                                    const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
                                    float* partial, int* counters, int n_seq, int n_head, int n_kv_head, int head_dim,
                                    int page_size, float scale, int window, int n_splits, void* stream) {
+    return lb_decode_attention_biased(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, n_seq, n_head, n_kv_head,
+                                      head_dim, page_size, scale, window, n_splits, nullptr, stream);
+}
+
+extern "C" int lb_decode_attention_biased(const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
+                                          int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
+                                          int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits, const float* distance,
+                                          void* stream) {
     LB_CHECK_ARG(n_seq >= 0 && n_splits >= 1, "decode attention: bad sizes n_seq=%d n_splits=%d", n_seq, n_splits);
     if (!lb_decode_attention_supports(n_head, n_kv_head, head_dim, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "decode attention: unsupported shape heads %d/%d head_dim %d page_size %d", n_head,
@@ -286,7 +303,7 @@ extern "C" int lb_decode_attention(const void* q, int64_t q_stride, const void* 
     auto s = static_cast<cudaStream_t>(stream);
 #define LB_HD(HD)                                                                                                     \
     return by_group<HD>(group, q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, \
-                        n_seq, n_kv_head, page_shift, scale, window, n_splits, s)
+                        n_seq, n_kv_head, page_shift, scale, window, n_splits, distance, s)
     switch (head_dim) {
         case 16: LB_HD(16);
         case 32: LB_HD(32);

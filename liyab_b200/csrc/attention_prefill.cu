@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(kThreads)
 prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache,
                          const int32_t* __restrict__ q_start, const int32_t* __restrict__ n_past,
                          const int32_t* __restrict__ block_table, int table_stride, __nv_bfloat16* __restrict__ out,
-                         int64_t out_stride, int n_head, int n_kv_head, int page_shift, float scale, int window) {
+                         int64_t out_stride, int n_head, int n_kv_head, int page_shift, float scale, int window,
+                         const float* __restrict__ distance) {
     constexpr int LD = HD + 8;                  // padded row of a tile in shared memory (elements)
     constexpr int CH = HD / 8;                  // 16-byte chunks per row
     constexpr int KS = HD / 16;                 // k-steps of Q K^T
@@ -142,6 +143,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
     for (int i = 0; i < OT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m_lo = -CUDART_INF_F, m_hi = -CUDART_INF_F, l_lo = 0.0f, l_hi = 0.0f;
     const float sc = scale * kLog2e;
+    // The head's pair (r1, r2) of the penalty by distance; in the scores' base-2 scale a key d positions back loses r1 log2(1 + r2 d).
+    const float r1 = distance != nullptr ? distance[head] : 0.0f, r2 = distance != nullptr ? distance[n_head + head] : 0.0f;
 
     for (int tile = 0; tile < n_tiles; ++tile) {
         const int stage = tile % kStages;
@@ -182,6 +185,10 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float v = s[nt][e] * sc;
+                if (distance != nullptr) {
+                    const int d = (e >= 2 ? pos_hi : pos_lo) - (j0 + nt * 8 + 2 * t + (e & 1));
+                    v = fmaf(-r1, __log2f(fmaf(r2, (float)max(d, 0), 1.0f)), v);
+                }
                 if (need_mask) {
                     const int j = j0 + nt * 8 + 2 * t + (e & 1);
                     const bool hi = e >= 2;
@@ -255,7 +262,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
 template <int HD>
 int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* q_start, const int32_t* n_past,
            const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len,
-           int n_head, int n_kv_head, int page_shift, float scale, int window, cudaStream_t s) {
+           int n_head, int n_kv_head, int page_shift, float scale, int window, const float* distance, cudaStream_t s) {
     constexpr size_t smem = (size_t)(kBM + 2 * kStages * kBN) * (HD + 8) * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
@@ -265,7 +272,7 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* q_
     dim3 grid((max_q_len + kBM - 1) / kBM, n_head, n_seq);
     LB_CHECK_CUDA(lb_launch_overlapped(prefill_attention_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, q_start, n_past, block_table, table_stride,
-        (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift, scale, window));
+        (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift, scale, window, distance));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
@@ -281,6 +288,14 @@ extern "C" int lb_prefill_attention(const void* q, int64_t q_stride, const void*
                                     const int32_t* n_past, const int32_t* block_table, int table_stride, void* out,
                                     int64_t out_stride, int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim,
                                     int page_size, float scale, int window, void* stream) {
+    return lb_prefill_attention_biased(q, q_stride, cache, q_start, n_past, block_table, table_stride, out, out_stride, n_seq, max_q_len, n_head, n_kv_head,
+                                       head_dim, page_size, scale, window, nullptr, stream);
+}
+
+extern "C" int lb_prefill_attention_biased(const void* q, int64_t q_stride, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                           const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len,
+                                           int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance,
+                                           void* stream) {
     LB_CHECK_ARG(n_seq >= 0 && max_q_len >= 0, "prefill attention: bad sizes");
     if (!lb_prefill_attention_supports(n_head, n_kv_head, head_dim, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "prefill attention: unsupported shape heads %d/%d head_dim %d page_size %d",
@@ -295,7 +310,7 @@ extern "C" int lb_prefill_attention(const void* q, int64_t q_stride, const void*
 #define LB_HD(HD)                                                                                                        \
     case HD:                                                                                                             \
         return launch<HD>(q, q_stride, cache, q_start, n_past, block_table, table_stride, out, out_stride, n_seq, max_q_len, \
-                          n_head, n_kv_head, page_shift, scale, window, s)
+                          n_head, n_kv_head, page_shift, scale, window, distance, s)
     switch (head_dim) {
         LB_HD(16);
         LB_HD(32);

@@ -107,7 +107,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int32_t* __restrict__ q_start, const int32_t* __restrict__ n_past,
                             const int32_t* __restrict__ block_table, int table_stride, __nv_bfloat16* __restrict__ out,
                             int64_t out_stride, int n_head, int n_kv_head, int page_shift, int kv_rows, float scale, int window,
-                            int* status) {
+                            const float* __restrict__ distance, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     lb_wait_for_predecessor();            // queries, keys and values come from the kernel before this one
@@ -255,6 +255,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos = past + tile_q * kBM + min(r, rows_here - 1);    // rows past the end copy the last one; not stored
         const int first = lb_first_visible(pos, window);
         const float sc = scale * kLog2e;
+        // The head's penalty by distance in the units of the raw scores (which are multiplied by sc later): a key d positions
+        // back loses r1 ln(1 + r2 d) / scale = pen log2(1 + r2 d).
+        const float pen = distance != nullptr ? distance[head] * 0.6931471805599453f / scale : 0.0f;
+        const float r2 = distance != nullptr ? distance[n_head + head] : 0.0f;
         const uint32_t swz = (uint32_t)(r & 7);
         uint8_t* p_row = p_s + (size_t)r * 128;
         float m = -CUDART_INF_F, l = 0.0f;                              // l: this thread's part of the row's sum
@@ -273,6 +277,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (ok) {
                 tmem_ld32(s_row, v);
                 tmem_ld_wait();
+                if (distance != nullptr) {
+                    // 1 + r2 (pos - j0 - i) = a0 - r2 i; keys after the query (masked below) are kept from an argument below zero.
+                    const float a0 = fmaf(r2, (float)(pos - j0), 1.0f);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        v[i] = __float_as_uint(fmaf(-pen, __log2f(fmaxf(fmaf(-r2, (float)i, a0), 1e-30f)), __uint_as_float(v[i])));
+                }
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
@@ -417,6 +428,15 @@ extern "C" int lb_prefill_attention_tc(const void* q, int64_t q_stride, int n_to
                                        const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
                                        int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len, int n_head,
                                        int n_kv_head, int head_dim, int page_size, float scale, int window, void* stream) {
+    return lb_prefill_attention_tc_biased(q, q_stride, n_tokens, cache, n_pages, q_start, n_past, block_table, table_stride, out, out_stride, n_seq, max_q_len,
+                                          n_head, n_kv_head, head_dim, page_size, scale, window, nullptr, stream);
+}
+
+extern "C" int lb_prefill_attention_tc_biased(const void* q, int64_t q_stride, int n_tokens, const void* cache, int n_pages, const int32_t* q_start,
+                                              const int32_t* n_past, const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
+                                              int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window,
+                                              const float* distance, void* stream) {
+    LB_CHECK_ARG(distance == nullptr || scale != 0.0f, "prefill attention (tcgen05): a penalty by distance needs a factor on the scores that is not zero");
     LB_CHECK_ARG(n_seq >= 0 && max_q_len >= 0 && n_tokens >= 0 && n_pages > 0, "prefill attention: bad sizes");
     if (!lb_prefill_attention_tc_supports(n_head, n_kv_head, head_dim, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "prefill attention (tcgen05): unsupported shape heads %d/%d head_dim %d page_size %d",
@@ -446,7 +466,7 @@ extern "C" int lb_prefill_attention_tc(const void* q, int64_t q_stride, int n_to
     dim3 grid(n_head * n_seq, (max_q_len + kBM - 1) / kBM);
     LB_CHECK_CUDA(lb_launch_overlapped(prefill_attention_tc_kernel, dim3(grid), dim3(kThreads), smem, static_cast<cudaStream_t>(stream), 
         map_q, map_kv, q_start, n_past, block_table, table_stride, (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift,
-        (int)kv_rows, scale, window, status));
+        (int)kv_rows, scale, window, distance, status));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

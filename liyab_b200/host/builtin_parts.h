@@ -113,8 +113,9 @@ public:
 inline void attend(StepContext& ctx, const Rows& q, void* cache, const GroupView& view, const Rows& att, const kernels::AttentionShape& a, int span) {
     const int T = ctx.n_tokens;
     const int n_pages = view.group->pool.num_pages();
-    if (ctx.runtime.dtype == DType::BF16 && ctx.decode_only && a.distance == nullptr) {
-        const bool tensor = kernels::decode_mma_supports(a), scalar = kernels::decode_scalar_supports(a);
+    if (ctx.runtime.dtype == DType::BF16 && ctx.decode_only) {
+        // A penalty by distance is a logarithm per score, which the scalar kernel has room for beside its loads.
+        const bool tensor = a.distance == nullptr && kernels::decode_mma_supports(a), scalar = kernels::decode_scalar_supports(a);
         if (tensor || scalar) {
             const int splits = kernels::decode_splits(T, a.n_kv_head, span, tensor);
             float* partial = nullptr;
@@ -129,7 +130,7 @@ inline void attend(StepContext& ctx, const Rows& q, void* cache, const GroupView
             return;
         }
     }
-    if (ctx.runtime.dtype == DType::BF16 && a.distance == nullptr && kernels::prefill_supports(a)) {
+    if (ctx.runtime.dtype == DType::BF16 && kernels::prefill_supports(a)) {
         kernels::prefill_attention(ctx.runtime, q, T, cache, n_pages, ctx.q_start, ctx.n_past, view.block_table, view.table_width,
                                    att, ctx.n_seq, ctx.max_q_len, a);
         return;

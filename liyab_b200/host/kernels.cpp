@@ -248,13 +248,14 @@ void decode_attention(cudaStream_t s, bool tensor_cores, const Rows& q, const vo
         throw invalid_argument("decode attention: q rows must be 16-byte aligned and a multiple of 8 elements apart");
     if (n_splits > 1 && (partial == nullptr || counters == nullptr))
         throw invalid_argument("decode attention: scratch buffers are missing");
+    if (tensor_cores && a.distance != nullptr) throw invalid_argument("decode attention: the tensor-core kernel takes no penalty by distance");
     if (tensor_cores)
         check(lb_decode_attention_mma(q.data, q.stride, cache, n_pages, positions, block_table, table_width, out.data, out.stride,
                                       partial, counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(),
                                       n_splits, s), "decode_attention_mma");
     else
-        check(lb_decode_attention(q.data, q.stride, cache, positions, block_table, table_width, out.data, out.stride, partial,
-                                  counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), n_splits, s),
+        check(lb_decode_attention_biased(q.data, q.stride, cache, positions, block_table, table_width, out.data, out.stride, partial,
+                                         counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), n_splits, a.distance, s),
               "decode_attention");
 }
 
@@ -267,14 +268,14 @@ void prefill_attention(const Runtime& rt, const Rows& q, int n_tokens, const voi
     // mma.sync kernel's several blocks per SM beyond that.
     const int64_t blocks = static_cast<int64_t>(n_seq) * a.n_head * ((max_q_len + 127) / 128);
     const bool tc = prefill_tc_supports(a) && q.stride % 8 == 0 && out.stride % 8 == 0 && aligned16(q.data) &&
-                    aligned16(out.data) && blocks <= 4 * static_cast<int64_t>(rt.sm_count);
+                    aligned16(out.data) && blocks <= 4 * static_cast<int64_t>(rt.sm_count) && a.scale > 0;     // it takes the maximum of the raw scores
     if (tc)
-        check(lb_prefill_attention_tc(q.data, q.stride, n_tokens, cache, n_pages, q_start, n_past, block_table, table_width,
-                                      out.data, out.stride, n_seq, max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size,
-                                      a.scale, a.mask(), rt.stream), "prefill_attention_tc");
+        check(lb_prefill_attention_tc_biased(q.data, q.stride, n_tokens, cache, n_pages, q_start, n_past, block_table, table_width,
+                                             out.data, out.stride, n_seq, max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size,
+                                             a.scale, a.mask(), a.distance, rt.stream), "prefill_attention_tc");
     else
-        check(lb_prefill_attention(q.data, q.stride, cache, q_start, n_past, block_table, table_width, out.data, out.stride, n_seq,
-                                   max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), rt.stream),
+        check(lb_prefill_attention_biased(q.data, q.stride, cache, q_start, n_past, block_table, table_width, out.data, out.stride, n_seq,
+                                          max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), a.distance, rt.stream),
               "prefill_attention");
 }
 
