@@ -49,6 +49,10 @@ _SIGNATURES = {
     "lb_prefill_attention_tc": [_p, _l, _i, _p, _i, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_prefill_attention_tc_supports": [_i, _i, _i, _i],
     "lb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _p],
+    "lb_paged_attention_generic_biased": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p, _p],
+    "lb_decode_attention_biased": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p],
+    "lb_prefill_attention_biased": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
+    "lb_prefill_attention_tc_biased": [_p, _l, _i, _p, _i, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
 }
 
 _lib = None
@@ -340,19 +344,26 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
 
 def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, tok_seq: torch.Tensor, positions: torch.Tensor,
                             block_table: torch.Tensor, out: torch.Tensor, n_tokens: int, n_head: int, n_kv_head: int,
-                            head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
-    """Causal attention of the step's tokens over their requests' pages, 32-bit arithmetic."""
+                            head_dim: int, page_size: int, scale: float, window: int = 0, distance: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of the step's tokens over their requests' pages, 32-bit arithmetic.  `distance` (float32, r1 [n_head] then
+    r2 [n_head]): the score of the key d positions back loses r1 ln(1 + r2 d)."""
     if q.dtype != cache.dtype or out.dtype != cache.dtype:
         raise invalid_argument("attention: q, cache and out must have one element type")
     if q.stride(1) != 1 or out.stride(1) != 1:
         raise invalid_argument("attention: q and out must be dense within a row")
-    check(lib().lb_paged_attention_generic(
+    check(lib().lb_paged_attention_generic_biased(
         _code(cache.dtype, "cache"), _dev(q, "q"), q.stride(0), _dev(cache, "cache"),
         _dev(tok_seq, "tok_seq", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
-        n_tokens, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), stream_ptr()),
+        n_tokens, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), _distance(distance, n_head), stream_ptr()),
         "paged_attention_generic")
     return out
+
+
+def _distance(distance: Optional[torch.Tensor], n_head: int) -> Optional[int]:
+    if distance is not None and (distance.numel() != 2 * n_head or not distance.is_contiguous()):
+        raise invalid_argument("attention: the penalty by distance is r1 [n_head] then r2 [n_head]")
+    return _opt(distance, "distance", torch.float32)
 
 
 def decode_attention_kernels(n_head: int, n_kv_head: int, head_dim: int, page_size: int) -> tuple:
@@ -382,9 +393,10 @@ def decode_splits(n_seq: int, n_kv_head: int, max_context: int = 0, tensor_cores
 def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                      out: torch.Tensor, partial: Optional[torch.Tensor], counters: Optional[torch.Tensor], n_seq: int,
                      n_head: int, n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int,
-                     n_splits: int, tensor_cores: Optional[bool] = None) -> torch.Tensor:
+                     n_splits: int, tensor_cores: Optional[bool] = None, distance: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one new token per request over its pages (bfloat16), keys split `n_splits` ways.
-    `tensor_cores`: None picks the tensor-core kernel where it takes the shape, else the scalar one."""
+    `tensor_cores`: None picks the tensor-core kernel where it takes the shape, else the scalar one.  `distance`: as for
+    paged_attention_generic; the scalar kernel takes it."""
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise invalid_argument("decode attention takes bfloat16 only")
     if q.stride(1) != 1 or out.stride(1) != 1 or q.stride(0) % 8 != 0 or q.data_ptr() % 16 != 0:
@@ -394,7 +406,16 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tens
         if partial is None or counters is None or partial.numel() < need or counters.numel() < n_seq * n_kv_head:
             raise invalid_argument("decode attention: scratch buffers are missing or too small")
     if tensor_cores is None:
-        tensor_cores = decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)[1]
+        tensor_cores = distance is None and decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)[1]
+    if distance is not None:
+        if tensor_cores:
+            raise invalid_argument("decode attention: the tensor-core kernel takes no penalty by distance")
+        check(lib().lb_decode_attention_biased(
+            _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(positions, "positions", torch.int32),
+            _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
+            _opt(partial, "partial", torch.float32), _opt(counters, "counters", torch.int32), n_seq, n_head, n_kv_head,
+            head_dim, page_size, float(scale), int(window), int(n_splits), _distance(distance, n_head), stream_ptr()), "decode_attention")
+        return out
     cache_args = (_dev(cache, "cache"), cache.shape[0]) if tensor_cores else (_dev(cache, "cache"),)
     fn = lib().lb_decode_attention_mma if tensor_cores else lib().lb_decode_attention
     check(fn(
@@ -426,9 +447,10 @@ def prefill_attention_tc_supports(n_head: int, n_kv_head: int, head_dim: int, pa
 def prefill_attention(q: torch.Tensor, cache: torch.Tensor, q_start: torch.Tensor, n_past: torch.Tensor,
                       block_table: torch.Tensor, out: torch.Tensor, n_seq: int, max_q_len: int, n_head: int,
                       n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int = 0,
-                      tcgen05: Optional[bool] = None) -> torch.Tensor:
+                      tcgen05: Optional[bool] = None, distance: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the step's prompt portions over their pages (bfloat16, tensor cores).  `tcgen05`: None picks
-    the tcgen05 kernel where it takes the shape and the rows are 16-byte aligned, else the mma.sync one."""
+    the tcgen05 kernel where it takes the shape and the rows are 16-byte aligned, else the mma.sync one.  `distance`: as for
+    paged_attention_generic."""
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise invalid_argument("prefill attention takes bfloat16 only")
     if q.stride(1) != 1 or out.stride(1) != 1:
@@ -442,17 +464,18 @@ def prefill_attention(q: torch.Tensor, cache: torch.Tensor, q_start: torch.Tenso
                    and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
                    and blocks <= 4 * _sm_count(q.device))
     if tcgen05:
-        check(lib().lb_prefill_attention_tc(
+        check(lib().lb_prefill_attention_tc_biased(
             _dev(q, "q"), q.stride(0), q.shape[0], _dev(cache, "cache"), cache.shape[0],
             _dev(q_start, "q_start", torch.int32), _dev(n_past, "n_past", torch.int32),
             _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0), n_seq,
-            max_q_len, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), stream_ptr()), "prefill_attention_tc")
+            max_q_len, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), _distance(distance, n_head), stream_ptr()),
+            "prefill_attention_tc")
         return out
-    check(lib().lb_prefill_attention(
+    check(lib().lb_prefill_attention_biased(
         _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(q_start, "q_start", torch.int32),
         _dev(n_past, "n_past", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.stride(0),
         _dev(out, "out"), out.stride(0), n_seq, max_q_len, n_head, n_kv_head, head_dim, page_size, float(scale),
-        int(window), stream_ptr()), "prefill_attention")
+        int(window), _distance(distance, n_head), stream_ptr()), "prefill_attention")
     return out
 
 
@@ -734,4 +757,59 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, gate_up: torch.Tensor,
     finally:
         lib().lb_expert_product_set_plain(0)
     check(lib().lb_expert_combine(_dev(x, "x", torch.float32), x.stride(0), _dev(y, "y"), y.stride(0), _dev(place, "place"), T, width, top, s), "expert_combine")
+    return ids, weights
+
+
+# ---- a sinusoid of the position, a gated norm in groups, gates with a cap, a router with a bias ---------------------------------------
+for _name, _args in {
+    "lb_embed_sinusoid": [_i, _p, _p, _p, _p, _p, _p, _i, _i, _f, _f, _p],
+    "lb_gated_group_norm": [_i, _p, _l, _p, _l, _p, _i, _p, _l, _p, _p, _l, _i, _i, _i, _f, _p],
+    "lb_gated_act_kind": [_i, _p, _l, _p, _l, _i, _i, _i, _f, _f, _p],
+    "lb_router_topk_biased": [_i, _p, _l, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+}.items():
+    _SIGNATURES[_name] = _args
+
+GATE_KINDS = {"sigmoid": 0, "silu": 1, "gelu_tanh": 2, "relu": 3, "capped": 4}
+
+
+def embed_sinusoid(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, base: float, gain: Optional[torch.Tensor], x: torch.Tensor,
+                   scale: float = 1.0, eps: float = 1e-6) -> torch.Tensor:
+    """x[t] = table[tokens[t]] * scale + e(positions[t]), e[2i] = sin(p w_i), e[2i+1] = cos(p w_i), w_i = base^(-2i / width); with `gain` the row
+    is then divided by its root mean square and multiplied by it.  The frequencies are made in double precision and passed as two floats each."""
+    width = table.shape[1]
+    w = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * torch.arange((width + 1) // 2, dtype=torch.float64) / width)
+    hi = w.to(torch.float32)
+    freq2 = torch.stack([hi, (w - hi.to(torch.float64)).to(torch.float32)], dim=1).contiguous().to(x.device)
+    check(lib().lb_embed_sinusoid(_code(table.dtype, "table"), _dev(tokens, "tokens", torch.int32), _dev(positions, "positions", torch.int32),
+                                  _dev(table, "table"), _dev(freq2, "freq2"), _opt(gain, "gain", torch.float32), _dev(x, "x", torch.float32), tokens.numel(),
+                                  width, float(scale), float(eps), stream_ptr()), "embed_sinusoid")
+    return x
+
+
+def gated_group_norm(o: torch.Tensor, skip: Optional[torch.Tensor], skip_gain: Optional[torch.Tensor], head: int, z: Optional[torch.Tensor],
+                     weight: Optional[torch.Tensor], out: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+    """out = (o + skip_gain[column / head] * skip) * silu(z), cut into `groups` equal parts each over its own root mean square, times weight."""
+    check(lib().lb_gated_group_norm(_code(out.dtype, "out"), _dev(o, "o", torch.float32), o.stride(0), _opt(skip, "skip", torch.float32),
+                                    skip.stride(0) if skip is not None else 0, _opt(skip_gain, "skip_gain", torch.float32), head,
+                                    _opt(z, "z", torch.float32), z.stride(0) if z is not None else 0, _opt(weight, "weight", torch.float32), _dev(out, "out"),
+                                    out.stride(0), o.shape[0], o.shape[1], groups, float(eps), stream_ptr()), "gated_group_norm")
+    return out
+
+
+def gated_act_kind(gu: torch.Tensor, out: torch.Tensor, gate: str, alpha: float = 0.0, limit: float = 0.0) -> torch.Tensor:
+    """out = gate(gu[:, :inner]) * gu[:, inner:]; "capped": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1)."""
+    inner = gu.shape[1] // 2
+    check(lib().lb_gated_act_kind(_code(out.dtype, "out"), _dev(gu, "gu", torch.float32), gu.stride(0), _dev(out, "out"), out.stride(0), gu.shape[0], inner,
+                                  GATE_KINDS[gate], float(alpha), float(limit), stream_ptr()), "gated_act")
+    return out
+
+
+def router_topk(h: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, softmax: bool, renormalise: bool):
+    """The `top` largest of router h + bias per row (32-bit sums, ties to the lower expert) and their weights.  Returns (ids, weights) [T, top]."""
+    T, width = h.shape
+    ids = torch.empty(T, top, dtype=torch.int32, device=h.device)
+    weights = torch.empty(T, top, dtype=torch.float32, device=h.device)
+    check(lib().lb_router_topk_biased(_code(h.dtype, "h"), _dev(h, "h"), h.stride(0), _dev(router, "router", h.dtype), _opt(bias, "bias", torch.float32),
+                                      _dev(ids, "ids"), _dev(weights, "weights"), T, router.shape[0], width, top, int(softmax), int(renormalise), stream_ptr()),
+          "router_topk")
     return ids, weights

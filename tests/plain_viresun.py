@@ -107,18 +107,20 @@ def state_space(h, W, p, m, eps, trace=None):
     C = xbc[:, inner + G * N:].reshape(n, G, N)
     dt = softplus(dt + W[p + "dt_bias"][None, :])
     decay = np.exp(-np.exp(W[p + "A_log"])[None, :] * dt)
-    y = np.zeros((n, H, E), dtype=h.dtype)
+    read = np.zeros((n, H, E), dtype=h.dtype)
     for a in range(H):
         g = a // (H // G)
         S = np.zeros((N, E), dtype=h.dtype)
         for t in range(n):
             S = decay[t, a] * S + dt[t, a] * np.outer(B[t, g], xs[t, a])
-            y[t, a] = S.T @ C[t, g] + W[p + "D"][a] * xs[t, a]
-    if trace is not None:
-        trace["memory"] = y.reshape(n, inner)
+            read[t, a] = S.T @ C[t, g]
+    y = read + W[p + "D"][None, :, None] * xs
     y = y.reshape(n, inner) * silu(z)
     parts = m["norm_groups"]
     y = rms(y.reshape(n, parts, inner // parts), eps).reshape(n, inner) * W[p + "norm"][None, :]
+    if trace is not None:
+        trace["memory"] = read.reshape(n, inner)          # what the state gives, before the skip, the gate and the norm
+        trace["state_space"] = y
     return y @ W[p + "o"].T
 
 
@@ -188,6 +190,8 @@ def layer_forward(x, W, config, i, trace=None):
         x = x + dense_ff(h, W, p + "mlp.")
     elif mlp["kind"] == "moe":
         x = x + routed_ff(h, W, p + "mlp.", mlp, trace)
+        if trace is not None:
+            trace["routed"] = x
     else:
         raise ValueError(mlp["kind"])
     return x
