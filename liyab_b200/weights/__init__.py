@@ -25,7 +25,7 @@ def bf16_to_f32(a: np.ndarray) -> np.ndarray:
 def f32_to_bf16(a: np.ndarray) -> np.ndarray:
     """Round to nearest even, as the library does."""
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
-    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16).reshape(np.shape(a))      # a single number keeps its shape ()
 
 
 def write_random_model(model_dir: str, raw_config: Mapping[str, Any], seed: int, dtype: str = "float32") -> str:
@@ -58,7 +58,7 @@ def write_safetensors(path: str, tensors: Mapping[str, np.ndarray], metadata: Op
     rev = {np.dtype(v): k for k, v in _NP.items() if k != "BF16"}
     names, dts, ranks, shapes, ptrs, keep = [], [], [], [], [], []
     for name, a in tensors.items():
-        a = np.ascontiguousarray(a)
+        a = np.ascontiguousarray(a).reshape(np.shape(a))      # ascontiguousarray gives a single number the shape (1,)
         keep.append(a)
         names.append(_capi.b(name))
         dts.append(_capi.b((tags or {}).get(name) or rev[a.dtype]))
