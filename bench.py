@@ -5,6 +5,7 @@
     python bench.py --impl reference        # the reference's own tools on this machine's CPU, or why they cannot run
     python bench.py --design puzutar [--size small]   # Puzutar at GPT-2's layer sizes beside GPT-2 itself (see puzutar_line)
     python bench.py --design vosurax [--size small]   # Vosurax likewise (see vosurax_line)
+    python bench.py --design viresun [--size small]   # Viresun beside Vosurax and GPT-2 (see viresun_line)
 
 A step is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (12 layers, width 768, 12 heads) with random weights, a batch of
@@ -398,6 +399,113 @@ def vosurax_line(args) -> int:
     return 0
 
 
+def viresun_config(size, layers=0):
+    """Viresun with the width, depth, head count, inner width and vocabulary of a GPT-2 size.  Of every four blocks the second is a state
+    space (inner width twice the model's, heads of 64 values, a state of 128 numbers, two groups, a convolution over 4 inputs, the norm
+    in two groups) with 16 experts of a quarter of the inner width, two a token, capped at 7; the others are attention under a window of
+    512 (heads of 64, a quarter as many key/value heads, a temperature that steps every 128 positions, a penalty by distance), the first
+    and third with a dense feed-forward, the fourth with the experts.  The last block runs on the second block's weights."""
+    g = SIZES[size]
+    L, W, H = max(4, layers or g["n_layer"]), g["n_embd"], g["n_head"]
+    attn = dict(heads=H, kv_heads=max(1, H // 4), dim=64, vdim=64, scale=0.125, mask=dict(size=512), q_temp=dict(coef=0.5, every=128))
+    ssm = dict(heads=2 * W // 64, vdim=64, state=128, groups=2, conv=4, norm_groups=2)
+    dense = dict(kind="dense", ff=g["n_inner"])
+    moe = dict(kind="moe", expert=dict(ff=g["n_inner"] // 4, limit=7.0), router=dict(experts=16, top=2))
+    blocks = []
+    for i in range(L):
+        if i % 4 == 1:
+            blocks.append(dict(type="mamba2", mixer=ssm, mlp=moe))
+        else:
+            blocks.append(dict(type="attention", mixer=attn, mlp=moe if i % 4 == 3 else dense))
+    blocks[-1] = dict(blocks[1], weights_of=1)
+    return dict(architecture="Viresun", vocab=g["vocab_size"], width=W, norm=dict(eps=1e-5), max_positions=g["n_positions"], layers=blocks)
+
+
+def viresun_bytes_and_flops(cfg, dtype_bytes, batch):
+    """Bytes a decode step of `batch` requests must read (weights its rows touch, states read and written, visible cache rows) and the
+    FLOPs of a prefill (products with the weights a token uses, attention inside its window, the states' updates and reads)."""
+    W, V = cfg["width"], cfg["vocab"]
+    step_bytes, token_flops, attn, mem = 2 * V * W * dtype_bytes, 2 * V * W, [], []
+    for l in cfg["layers"]:
+        m, mlp = l["mixer"], l["mlp"]
+        if l["type"] == "mamba2":
+            inner, GN = m["heads"] * m["vdim"], m["groups"] * m["state"]
+            mats = W * (2 * inner + 2 * GN + m["heads"]) + W * inner
+            mem.append((m["heads"], m["state"], m["vdim"], (m["conv"] - 1) * (inner + 2 * GN)))
+        else:
+            mats = W * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"])) + W * m["heads"] * m["vdim"]
+            attn.append((m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]))
+        used = touched = mats
+        if mlp and mlp["kind"] == "dense":
+            used += 3 * W * mlp["ff"]
+            touched += 3 * W * mlp["ff"]
+        elif mlp:
+            E, top, F = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+            used += E * W + 3 * W * top * F
+            touched += E * W + 3 * W * F * E * (1.0 - (1.0 - top / E) ** batch)      # the experts a batch is expected to touch
+        token_flops += 2 * used
+        step_bytes += touched * dtype_bytes
+    state_bytes = sum(2 * 4 * (H * N * E + conv) for H, N, E, conv in mem)
+    cache_row_bytes = [dtype_bytes * 2 * G * max(D, E) for _, G, D, E, _ in attn]
+
+    def decode_bytes(mean_context):
+        return step_bytes + batch * (state_bytes + sum(b * min(mean_context, c) for b, (_, _, _, _, c) in zip(cache_row_bytes, attn)))
+
+    def prefill_flops(seq_lens, rows):
+        total = sum(seq_lens) * (token_flops - 2 * V * W) + 2 * rows * V * W
+        for H, G, D, E, c in attn:
+            total += sum(2 * H * (D + E) * sum(min(i + 1, c) for i in range(s)) for s in seq_lens)
+        for H, N, E, _ in mem:
+            total += sum(seq_lens) * 4 * H * N * E
+        return total
+
+    return decode_bytes, prefill_flops
+
+
+def design_block(folder, dtype, steps, pk, bytes_and_flops):
+    """Decode at batch 1 / 8 / 64 (512-token prompts) and a prefill of 2 x 1,024 tokens of the model in `folder`, device-timed by the library's
+    own measurement; `bytes_and_flops(batch)` gives the step's bytes and the prefill's FLOPs for the fractions of the measured peaks."""
+    from liyab_b200.engine import Replayer
+    rep = Replayer(folder, dtype, max_tokens=64 * 1024, max_requests=64, cuda_graphs=True, max_step_tokens=PREFILL_TOKENS)
+    block = {}
+    for b in (1, 8, 64):
+        decode_bytes, flops = bytes_and_flops(b)
+        r = rep.bench_decode(b, PROMPT_LEN, steps, 3, 0)
+        achieved = decode_bytes(r["mean_context"]) / (r["ms_per_step"] / 1e3) / 1e9
+        r.update(tok_s=b / (r["ms_per_step"] / 1e3), frac=achieved / pk["hbm_gbs"])
+        block[f"decode_b{b}"] = detail(r) | {"launches_per_step": r["kernel_launches"] // steps}
+    n_seq = PREFILL_TOKENS // 1024
+    r = rep.bench_prefill(n_seq, 1024, 5)
+    peak = pk["bf16_tflops"] if dtype == "bfloat16" else FP32_TFLOPS_NOMINAL
+    block["prefill"] = {"value": round(PREFILL_TOKENS / (r["ms_per_step"] / 1e3), 1), "ms": round(r["ms_per_step"], 4),
+                        "frac": round(flops([1024] * n_seq, n_seq) / (r["ms_per_step"] / 1e3) / 1e12 / peak, 4), "launches": r["kernel_launches"]}
+    rep.close()
+    return block
+
+
+def viresun_line(args) -> int:
+    """--design viresun: decode (batch 1 / 8 / 64, 512-token prompts) and prefill (2 x 1024 tokens) of Viresun at the layer sizes of
+    GPT-2 `--size`, and the same four figures of Vosurax (the engine's closest design: attention under a mask, a matrix state per head,
+    routed experts) and of GPT-2 at that size."""
+    from liyab_b200.weights import write_random_model
+    pk = peaks()
+    dtype_bytes = 2 if args.dtype == "bfloat16" else 4
+    cfg = viresun_config(args.size, args.layers)
+    steps = min(args.steps, 128)
+    out = {"design": "viresun", "size": args.size, "dtype": args.dtype, "peaks": pk["source"],
+           "config": {k: cfg[k] for k in ("width", "vocab", "norm")} | {"layers": len(cfg["layers"]), "attention": cfg["layers"][0], "state_space": cfg["layers"][1]}}
+    with tempfile.TemporaryDirectory(prefix="liyab_b200_bench_") as tmp:
+        folder = write_random_model(os.path.join(tmp, "viresun"), cfg, seed=0, dtype=args.dtype)
+        out["viresun"] = design_block(folder, args.dtype, steps, pk, lambda b: viresun_bytes_and_flops(cfg, dtype_bytes, b))
+        other = vosurax_config(args.size, args.layers + 2 if args.layers else 0)
+        folder = write_random_model(os.path.join(tmp, "vosurax"), other, seed=0, dtype=args.dtype)
+        out["vosurax"] = design_block(folder, args.dtype, steps, pk, lambda b: vosurax_bytes_and_flops(other, dtype_bytes, b))
+        if not args.layers:
+            out["gpt2"], _ = size_block(tmp, args.size, args.dtype, steps, pk)
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm(args) -> int:
     from baseline.reference_arm import run
     return run(args)
@@ -415,8 +523,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="the headline figure only")
     ap.add_argument("--no-extra", action="store_true", help="skip the 32-bit engine, the other sizes and the mixed workload")
-    ap.add_argument("--design", default="gpt2", choices=["gpt2", "puzutar", "vosurax"],
-                    help="puzutar, vosurax: that design at the layer sizes of GPT-2 --size beside GPT-2 itself (its own JSON line; the default run is unchanged)")
+    ap.add_argument("--design", default="gpt2", choices=["gpt2", "puzutar", "vosurax", "viresun"],
+                    help="puzutar, vosurax, viresun: that design at the layer sizes of GPT-2 --size beside GPT-2 itself (its own JSON line; the default run is unchanged)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -424,6 +532,8 @@ def main() -> int:
         return puzutar_line(args)
     if args.design == "vosurax":
         return vosurax_line(args)
+    if args.design == "viresun":
+        return viresun_line(args)
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (run with --gpus 1)")
         return 2
