@@ -143,6 +143,10 @@ int lb_decode_attention_mma(const void* q, int64_t q_stride, const void* cache, 
                             int* counters, int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale,
                             int window, int n_splits, void* stream);
 int lb_decode_attention_mma_supports(int n_head, int n_kv_head, int head_dim, int page_size);
+int lb_decode_attention_mma_biased(const void* q, int64_t q_stride, const void* cache, int n_pages, const int32_t* positions,
+                                   const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial, int* counters,
+                                   int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits,
+                                   const float* distance, void* stream);
 int64_t lb_decode_attention_scratch_floats(int n_seq, int n_head, int head_dim, int n_splits);
 
 /* Prefill attention, bfloat16, products on the tensor cores: request i brings the

@@ -74,7 +74,7 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
                             const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride,
                             __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ partial,
                             int* __restrict__ counters, int n_head, int n_kv_head, int page_shift, float scale, int window,
-                            int n_splits, int cluster_merge) {
+                            int n_splits, int cluster_merge, const float* __restrict__ distance) {
     constexpr int kThreads = kWarps * 32;
     constexpr int LD = HD;                      // a tile's row in shared memory; its 16-byte chunks are XOR-swizzled by the row
     constexpr int CH = HD / 8;                  // 16-byte chunks per row
@@ -165,6 +165,11 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
     for (int i = 0; i < OT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m_lo = -CUDART_INF_F, m_hi = -CUDART_INF_F, l_lo = 0.0f, l_hi = 0.0f;
     const float sc = scale * kLog2e;
+    // The pairs (r1, r2) of the penalty by distance of this thread's two rows (query heads kvh G + g and + 8); in the scores' base-2
+    // scale a key d positions back loses r1 log2(1 + r2 d).  Weights: read before the wait for the kernel before this one.
+    const bool biased = distance != nullptr;
+    const float r1_lo = biased && g < G ? distance[kvh * G + g] : 0.0f, r2_lo = biased && g < G ? distance[n_head + kvh * G + g] : 0.0f;
+    const float r1_hi = biased && g + 8 < G ? distance[kvh * G + g + 8] : 0.0f, r2_hi = biased && g + 8 < G ? distance[n_head + kvh * G + g + 8] : 0.0f;
 
     if constexpr (TMA) {
         if (lane == 0) {
@@ -238,7 +243,9 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int j = j0 + nt * 8 + 2 * t + (e & 1);
-                s[nt][e] = (j >= begin && j < end) ? s[nt][e] * sc : -CUDART_INF_F;
+                float v = s[nt][e] * sc;
+                if (biased) v = fmaf(-(e >= 2 ? r1_hi : r1_lo), __log2f(fmaf(e >= 2 ? r2_hi : r2_lo, (float)max(pos - j, 0), 1.0f)), v);
+                s[nt][e] = (j >= begin && j < end) ? v : -CUDART_INF_F;
             }
             mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
             mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
@@ -424,7 +431,7 @@ struct Variant {
 
     static int launch(const CUtensorMap& map_kv, int kv_rows, int* status, const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
                       int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
-                      int n_kv_head, int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
+                      int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, cudaStream_t s) {
         dim3 grid(n_splits, n_kv_head, n_seq);
         // Two to eight key ranges: the ranges of a request and head form a cluster and merge in shared memory.
         const int group = n_head / n_kv_head;
@@ -437,7 +444,7 @@ struct Variant {
                                                    dim3(kWarps * 32), smem + inbox, s, map_kv, kv_rows, status, (const __nv_bfloat16*)q,
                                                    q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
                                                    (__nv_bfloat16*)out, out_stride, partial, counters, n_head, n_kv_head, page_shift,
-                                                   scale, window, n_splits, cluster ? 1 : 0));
+                                                   scale, window, n_splits, cluster ? 1 : 0, distance));
         return LB_OK;
     }
 };
@@ -449,7 +456,7 @@ struct Variant {
 template <int HD, bool TMA>
 int launch_for(const CUtensorMap& map_kv, int kv_rows, int* status, const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
                int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
-               int n_kv_head, int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
+               int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, cudaStream_t s) {
     using Wide = Variant<HD, 4, 2, TMA>;
     using Narrow = Variant<HD, 2, 2, TMA>;
     static int n_sm = 0;
@@ -468,9 +475,9 @@ int launch_for(const CUtensorMap& map_kv, int kv_rows, int* status, const void* 
     const bool narrow = blocks > slots_wide && waves_wide * slots_wide >= waves_narrow * slots_narrow;
     if (narrow)
         return Narrow::launch(map_kv, kv_rows, status, q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters,
-                              n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, s);
+                              n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, s);
     return Wide::launch(map_kv, kv_rows, status, q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, n_seq,
-                        n_head, n_kv_head, page_shift, scale, window, n_splits, s);
+                        n_head, n_kv_head, page_shift, scale, window, n_splits, distance, s);
 }
 
 }  // namespace
@@ -489,6 +496,14 @@ extern "C" int lb_decode_attention_mma(const void* q, int64_t q_stride, const vo
                                        const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
                                        float* partial, int* counters, int n_seq, int n_head, int n_kv_head, int head_dim,
                                        int page_size, float scale, int window, int n_splits, void* stream) {
+    return lb_decode_attention_mma_biased(q, q_stride, cache, n_pages, positions, block_table, table_stride, out, out_stride, partial, counters, n_seq, n_head,
+                                          n_kv_head, head_dim, page_size, scale, window, n_splits, nullptr, stream);
+}
+
+extern "C" int lb_decode_attention_mma_biased(const void* q, int64_t q_stride, const void* cache, int n_pages, const int32_t* positions,
+                                              const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial, int* counters,
+                                              int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits,
+                                              const float* distance, void* stream) {
     LB_CHECK_ARG(n_seq >= 0 && n_splits >= 1, "decode attention: bad sizes n_seq=%d n_splits=%d", n_seq, n_splits);
     if (!lb_decode_attention_mma_supports(n_head, n_kv_head, head_dim, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "decode attention (tensor cores): unsupported shape heads %d/%d head_dim %d page_size %d",
@@ -512,11 +527,11 @@ extern "C" int lb_decode_attention_mma(const void* q, int64_t q_stride, const vo
             if (rc != LB_OK) return rc;
             return launch_for<64, true>(map_kv, (int)kv_rows, status, q, q_stride, cache, positions, block_table, table_stride,
                                         out, out_stride, partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window,
-                                        n_splits, s);
+                                        n_splits, distance, s);
         }
         return launch_for<64, false>(none, 0, nullptr, q, q_stride, cache, positions, block_table, table_stride, out, out_stride,
-                                     partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, s);
+                                     partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, s);
     }
     return launch_for<128, false>(none, 0, nullptr, q, q_stride, cache, positions, block_table, table_stride, out, out_stride,
-                                  partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, s);
+                                  partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, s);
 }

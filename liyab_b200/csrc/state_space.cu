@@ -49,13 +49,15 @@ __global__ void __launch_bounds__(256) ssm_prepare_kernel(PrepareArgs a) {
     const float* row = a.proj + (size_t)t * a.ld;
     float* out = a.out + (size_t)t * a.ldo;
     float* st = a.state + (size_t)a.slots[seq] * a.slot_stride;
+    // A row's channels are spread over the blocks (row, 0 .. gridDim.y - 1): every block makes the heads' steps for itself, the
+    // first one writes them.
     for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
         const float dt = lb_softplus(row[a.dt_off + h] + (a.dt_bias != nullptr ? a.dt_bias[h] : 0.0f));
         dt_s[h] = dt;
-        out[2 * inner + a.GN2 + h] = -expf(a.a_log[h]) * dt;
+        if (blockIdx.y == 0) out[2 * inner + a.GN2 + h] = -expf(a.a_log[h]) * dt;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         const float* w = a.taps + (size_t)c * K;
         float acc = a.tap_bias != nullptr ? a.tap_bias[c] : 0.0f;
         for (int j = 0; j < K; ++j) {
@@ -152,9 +154,9 @@ extern "C" int lb_ssm_prepare(const float* proj, int64_t ld, int xbc_off, int dt
     auto s = static_cast<cudaStream_t>(stream);
     PrepareArgs a{proj, ld, xbc_off, dt_off, taps, tap_bias, dt_bias, a_log, state, slot_stride, tok_seq, q_start, slots, out, ldo,
                   n_head, vdim, group_values, n_taps, decode_only ? 1 : 0};
-    LB_CHECK_CUDA(lb_launch_overlapped(ssm_prepare_kernel, dim3(n_tokens), dim3(256), (size_t)n_head * sizeof(float), s, a));
+    const int by = (channels + 255) / 256;
+    LB_CHECK_CUDA(lb_launch_overlapped(ssm_prepare_kernel, dim3(n_tokens, by < 64 ? by : 64), dim3(256), (size_t)n_head * sizeof(float), s, a));
     if (!decode_only && n_taps > 1) {
-        const int by = (channels + 255) / 256;
         LB_CHECK_CUDA(lb_launch_overlapped(ssm_conv_state_kernel, dim3(n_seq, by), dim3(256), 0, s, proj, ld, xbc_off, state, slot_stride, q_start, slots,
                                            channels, n_taps));
     }

@@ -114,8 +114,7 @@ inline void attend(StepContext& ctx, const Rows& q, void* cache, const GroupView
     const int T = ctx.n_tokens;
     const int n_pages = view.group->pool.num_pages();
     if (ctx.runtime.dtype == DType::BF16 && ctx.decode_only) {
-        // A penalty by distance is a logarithm per score, which the scalar kernel has room for beside its loads.
-        const bool tensor = a.distance == nullptr && kernels::decode_mma_supports(a), scalar = kernels::decode_scalar_supports(a);
+        const bool tensor = kernels::decode_mma_supports(a), scalar = kernels::decode_scalar_supports(a);
         if (tensor || scalar) {
             const int splits = kernels::decode_splits(T, a.n_kv_head, span, tensor);
             float* partial = nullptr;

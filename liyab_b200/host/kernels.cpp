@@ -248,11 +248,10 @@ void decode_attention(cudaStream_t s, bool tensor_cores, const Rows& q, const vo
         throw invalid_argument("decode attention: q rows must be 16-byte aligned and a multiple of 8 elements apart");
     if (n_splits > 1 && (partial == nullptr || counters == nullptr))
         throw invalid_argument("decode attention: scratch buffers are missing");
-    if (tensor_cores && a.distance != nullptr) throw invalid_argument("decode attention: the tensor-core kernel takes no penalty by distance");
     if (tensor_cores)
-        check(lb_decode_attention_mma(q.data, q.stride, cache, n_pages, positions, block_table, table_width, out.data, out.stride,
-                                      partial, counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(),
-                                      n_splits, s), "decode_attention_mma");
+        check(lb_decode_attention_mma_biased(q.data, q.stride, cache, n_pages, positions, block_table, table_width, out.data, out.stride,
+                                             partial, counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(),
+                                             n_splits, a.distance, s), "decode_attention_mma");
     else
         check(lb_decode_attention_biased(q.data, q.stride, cache, positions, block_table, table_width, out.data, out.stride, partial,
                                          counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), n_splits, a.distance, s),

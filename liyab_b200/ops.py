@@ -51,6 +51,7 @@ _SIGNATURES = {
     "lb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _p],
     "lb_paged_attention_generic_biased": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p, _p],
     "lb_decode_attention_biased": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p],
+    "lb_decode_attention_mma_biased": [_p, _l, _p, _i, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p],
     "lb_prefill_attention_biased": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
     "lb_prefill_attention_tc_biased": [_p, _l, _i, _p, _i, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
 }
@@ -396,7 +397,7 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tens
                      n_splits: int, tensor_cores: Optional[bool] = None, distance: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one new token per request over its pages (bfloat16), keys split `n_splits` ways.
     `tensor_cores`: None picks the tensor-core kernel where it takes the shape, else the scalar one.  `distance`: as for
-    paged_attention_generic; the scalar kernel takes it."""
+    paged_attention_generic."""
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise invalid_argument("decode attention takes bfloat16 only")
     if q.stride(1) != 1 or out.stride(1) != 1 or q.stride(0) % 8 != 0 or q.data_ptr() % 16 != 0:
@@ -406,23 +407,14 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tens
         if partial is None or counters is None or partial.numel() < need or counters.numel() < n_seq * n_kv_head:
             raise invalid_argument("decode attention: scratch buffers are missing or too small")
     if tensor_cores is None:
-        tensor_cores = distance is None and decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)[1]
-    if distance is not None:
-        if tensor_cores:
-            raise invalid_argument("decode attention: the tensor-core kernel takes no penalty by distance")
-        check(lib().lb_decode_attention_biased(
-            _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(positions, "positions", torch.int32),
-            _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
-            _opt(partial, "partial", torch.float32), _opt(counters, "counters", torch.int32), n_seq, n_head, n_kv_head,
-            head_dim, page_size, float(scale), int(window), int(n_splits), _distance(distance, n_head), stream_ptr()), "decode_attention")
-        return out
+        tensor_cores = decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)[1]
     cache_args = (_dev(cache, "cache"), cache.shape[0]) if tensor_cores else (_dev(cache, "cache"),)
-    fn = lib().lb_decode_attention_mma if tensor_cores else lib().lb_decode_attention
+    fn = lib().lb_decode_attention_mma_biased if tensor_cores else lib().lb_decode_attention_biased
     check(fn(
         _dev(q, "q"), q.stride(0), *cache_args, _dev(positions, "positions", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
         _opt(partial, "partial", torch.float32), _opt(counters, "counters", torch.int32), n_seq, n_head, n_kv_head,
-        head_dim, page_size, float(scale), int(window), int(n_splits), stream_ptr()), "decode_attention")
+        head_dim, page_size, float(scale), int(window), int(n_splits), _distance(distance, n_head), stream_ptr()), "decode_attention")
     return out
 
 
