@@ -408,14 +408,30 @@ public:
         const int T = ctx.n_tokens;
         const Rows gu = ctx.workspace->get("gated.gate_up", T, 2 * inner, DType::F32);
         gate_up.forward(ctx, h, gu, T);
-        const Rows mid = ctx.workspace->get("gated.inner", T, inner, ctx.runtime.dtype);
-        kernels::gated_act(ctx.stream(), gu, mid, T, gate, alpha, limit);
-        down.forward(ctx, mid, x, T, kernels::kNone, &x);
+        finish(ctx, gu, x);
+    }
+    // As the dense feed-forward's: the [gate | up] product of a few tokens normalises the rows inside its kernel.
+    bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x) override {
+        const int T = ctx.n_tokens;
+        if (gate_up.bias != nullptr || !kernels::gemm_rows_normed_supports(ctx.runtime, x_in, gate_up.weight, T)) return false;
+        const Rows gu = ctx.workspace->get("gated.gate_up", T, 2 * inner, DType::F32);
+        kernels::gemm_rows_normed(ctx.stream(), x_in, norm.gain, norm.offset, norm.eps, gate_up.weight, nullptr, gu, T, kernels::kNone, nullptr, nullptr,
+                                  norm.rms, norm.gain_offset);
+        finish(ctx, gu, x);
+        return true;
     }
     int64_t inner;
     int gate;
     float alpha, limit;
     Linear gate_up, down;
+
+private:
+    void finish(StepContext& ctx, const Rows& gu, const Rows& x) {
+        const int T = ctx.n_tokens;
+        const Rows mid = ctx.workspace->get("gated.inner", T, inner, ctx.runtime.dtype);
+        kernels::gated_act(ctx.stream(), gu, mid, T, gate, alpha, limit);
+        down.forward(ctx, mid, x, T, kernels::kNone, &x);
+    }
 };
 
 // ---- routed experts --------------------------------------------------------------------------------------------------

@@ -251,7 +251,9 @@ std::map<std::string, HostTensor> load_parameters(const std::string& model_dir, 
             const TensorEntry* e = files.find(full);
             if (e == nullptr) { missing.push_back(std::format("missing tensor '{}'", full)); continue; }
             used.insert(full);
-            if (e->shape != src.shape)
+            // A single number that is to be repeated may be stored without a shape or as one entry.
+            const bool one_number = spec.repeat > 0 && shape_numel(e->shape) == 1 && e->shape.size() <= 1;
+            if (e->shape != src.shape && !one_number)
                 wrong.push_back(std::format("tensor '{}' has shape {}, expected {}", full, shape_text(e->shape), shape_text(src.shape)));
             else if (!is_float(e->dtype) && spec.kind != ParamKind::Index)
                 wrong.push_back(std::format("tensor '{}' has dtype {}, expected a floating type", full, dtype_name(e->dtype)));

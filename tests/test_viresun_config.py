@@ -111,3 +111,18 @@ def test_bad_configurations_are_refused(damage, text):
     with pytest.raises(LiyabError) as e:
         describe_config(c)
     assert text in str(e.value)
+
+
+def test_a_single_number_may_be_stored_without_a_shape_or_as_one_entry(tmp_path):
+    """A norm's gain is one number for all coordinates; the file may hold it with the shape [] or [1], and the loader repeats it."""
+    import numpy as np
+    from liyab_b200.weights import load_parameters
+    from viresun_models import random_weights, write_model
+    weights = random_weights(CONFIG_D, 7)
+    assert any(np.asarray(v).ndim == 0 for v in weights.values())
+    as_lists = {k: (np.asarray(v).reshape(1) if np.asarray(v).ndim == 0 else v) for k, v in weights.items()}
+    first = load_parameters(write_model(str(tmp_path / "plain"), CONFIG_D, weights))
+    second = load_parameters(write_model(str(tmp_path / "lists"), CONFIG_D, as_lists))
+    assert first.keys() == second.keys() and all(np.array_equal(first[k], second[k]) for k in first)
+    gain = first["final_norm.weight"]
+    assert gain.shape == (CONFIG_D["width"],) and np.all(gain == gain[0]) and gain[0] == np.float32(weights["final.norm"])

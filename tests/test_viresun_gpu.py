@@ -430,3 +430,4 @@ def test_command_line_and_sampling(models):
         draws.append(engine.generate_tokens(prompt, SamplingParams(max_tokens=12, temperature=0.9, top_k=20, top_p=0.95, seed=seed)).tokens)
         engine.close()
     assert draws[0] == draws[1] and draws[0] != draws[2] and all(0 <= t < config["vocab"] for t in draws[2])
+
