@@ -10,6 +10,7 @@
 //                         tokens does it in lb_ssm_prepare).
 //   lb_gated_group_norm   y = (o + D[head] x) * silu(z), cut into equal groups each over its own root mean square, times a gain.
 //
+// lb_ssm_prepare has a form with a channel a thread for any sizes and one with four channels a thread for rows on 16-byte borders.
 // Everything is 32-bit: the convolution's inputs stay the float sums of the projection, so a row's result does not depend on
 // where its sequence was cut.
 #include "api.h"
@@ -71,6 +72,65 @@ __global__ void __launch_bounds__(256) ssm_prepare_kernel(PrepareArgs a) {
         if (a.update_state) {
             for (int r = 0; r + 1 < K - 1; ++r) st[(size_t)r * channels + c] = st[(size_t)(r + 1) * channels + c];
             if (K > 1) st[(size_t)(K - 2) * channels + c] = row[a.xbc_off + c];
+        }
+    }
+}
+
+// The same four channels a thread, where every row, the state and the output start on 16 bytes and a head's values are a multiple
+// of four (so four channels share a step): 16-byte loads and stores, a quarter of the instructions.  KT = 4: the taps of a channel are
+// one 16-byte load and the loop over them is unrolled; KT = 0: any number of taps.
+template <int KT>
+__global__ void __launch_bounds__(256) ssm_prepare_vec4_kernel(PrepareArgs a) {
+    extern __shared__ float dt_s[];      // [H]
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, seq = a.tok_seq[t];
+    const int first = a.q_start[seq], i = t - first;
+    const int inner = a.H * a.E, channels = inner + a.GN2, K = KT > 0 ? KT : a.K;
+    const float* row = a.proj + (size_t)t * a.ld;
+    float* out = a.out + (size_t)t * a.ldo;
+    float* st = a.state + (size_t)a.slots[seq] * a.slot_stride;
+    for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
+        const float dt = lb_softplus(row[a.dt_off + h] + (a.dt_bias != nullptr ? a.dt_bias[h] : 0.0f));
+        dt_s[h] = dt;
+        if (blockIdx.y == 0) out[2 * inner + a.GN2 + h] = -expf(a.a_log[h]) * dt;
+    }
+    __syncthreads();
+    for (int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x); c < channels; c += 4 * gridDim.y * blockDim.x) {
+        float4 acc = a.tap_bias != nullptr ? *reinterpret_cast<const float4*>(a.tap_bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float* w = a.taps + (size_t)c * K;
+        auto input = [&](int j) {
+            const int idx = i - (K - 1) + j;       // the input's place in the portion; negative: in the state
+            return idx >= 0 ? *reinterpret_cast<const float4*>(a.proj + (size_t)(first + idx) * a.ld + a.xbc_off + c)
+                            : *reinterpret_cast<const float4*>(st + (size_t)(K - 1 + idx) * channels + c);
+        };
+        if constexpr (KT == 4) {
+            const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
+            const float4 w2 = *reinterpret_cast<const float4*>(w + 8), w3 = *reinterpret_cast<const float4*>(w + 12);
+            const float4 u0 = input(0), u1 = input(1), u2 = input(2), u3 = input(3);
+            acc.x = fmaf(w0.w, u3.x, fmaf(w0.z, u2.x, fmaf(w0.y, u1.x, fmaf(w0.x, u0.x, acc.x))));
+            acc.y = fmaf(w1.w, u3.y, fmaf(w1.z, u2.y, fmaf(w1.y, u1.y, fmaf(w1.x, u0.y, acc.y))));
+            acc.z = fmaf(w2.w, u3.z, fmaf(w2.z, u2.z, fmaf(w2.y, u1.z, fmaf(w2.x, u0.z, acc.z))));
+            acc.w = fmaf(w3.w, u3.w, fmaf(w3.z, u2.w, fmaf(w3.y, u1.w, fmaf(w3.x, u0.w, acc.w))));
+        } else {
+            for (int j = 0; j < K; ++j) {
+                const float4 u = input(j);
+                acc.x = fmaf(w[j], u.x, acc.x);
+                acc.y = fmaf(w[K + j], u.y, acc.y);
+                acc.z = fmaf(w[2 * K + j], u.z, acc.z);
+                acc.w = fmaf(w[3 * K + j], u.w, acc.w);
+            }
+        }
+        const float4 y = make_float4(ss_silu(acc.x), ss_silu(acc.y), ss_silu(acc.z), ss_silu(acc.w));
+        *reinterpret_cast<float4*>(out + c) = y;
+        if (c < inner) {
+            const float dt = dt_s[c / a.E];
+            *reinterpret_cast<float4*>(out + inner + a.GN2 + c) = make_float4(dt * y.x, dt * y.y, dt * y.z, dt * y.w);
+        }
+        if (a.update_state) {
+            for (int r = 0; r + 1 < K - 1; ++r)
+                *reinterpret_cast<float4*>(st + (size_t)r * channels + c) = *reinterpret_cast<const float4*>(st + (size_t)(r + 1) * channels + c);
+            if (K > 1) *reinterpret_cast<float4*>(st + (size_t)(K - 2) * channels + c) = *reinterpret_cast<const float4*>(row + a.xbc_off + c);
         }
     }
 }
@@ -155,7 +215,17 @@ extern "C" int lb_ssm_prepare(const float* proj, int64_t ld, int xbc_off, int dt
     PrepareArgs a{proj, ld, xbc_off, dt_off, taps, tap_bias, dt_bias, a_log, state, slot_stride, tok_seq, q_start, slots, out, ldo,
                   n_head, vdim, group_values, n_taps, decode_only ? 1 : 0};
     const int by = (channels + 255) / 256;
-    LB_CHECK_CUDA(lb_launch_overlapped(ssm_prepare_kernel, dim3(n_tokens, by < 64 ? by : 64), dim3(256), (size_t)n_head * sizeof(float), s, a));
+    auto on16 = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool vec4 = vdim % 4 == 0 && group_values % 4 == 0 && ld % 4 == 0 && xbc_off % 4 == 0 && ldo % 4 == 0 && slot_stride % 4 == 0 && on16(proj) &&
+                      on16(out) && on16(state) && on16(tap_bias) && (n_taps != 4 || on16(taps));
+    if (vec4) {
+        const int bq = (channels / 4 + 255) / 256;
+        const dim3 grid(n_tokens, bq < 64 ? bq : 64);
+        if (n_taps == 4) LB_CHECK_CUDA(lb_launch_overlapped(ssm_prepare_vec4_kernel<4>, grid, dim3(256), (size_t)n_head * sizeof(float), s, a));
+        else LB_CHECK_CUDA(lb_launch_overlapped(ssm_prepare_vec4_kernel<0>, grid, dim3(256), (size_t)n_head * sizeof(float), s, a));
+    } else {
+        LB_CHECK_CUDA(lb_launch_overlapped(ssm_prepare_kernel, dim3(n_tokens, by < 64 ? by : 64), dim3(256), (size_t)n_head * sizeof(float), s, a));
+    }
     if (!decode_only && n_taps > 1) {
         LB_CHECK_CUDA(lb_launch_overlapped(ssm_conv_state_kernel, dim3(n_seq, by), dim3(256), 0, s, proj, ld, xbc_off, state, slot_stride, q_start, slots,
                                            channels, n_taps));

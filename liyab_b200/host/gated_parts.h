@@ -177,9 +177,13 @@ private:
         const Rows att = ws.get("gated_attention.att", T, static_cast<int64_t>(H) * P, dt);
         const int reach = shape.chunk > 0 ? shape.chunk : shape.window;
         attend(ctx, q, cache, *view, att, a, reach > 0 ? std::min(reach, ctx.max_positions) : ctx.max_positions);
-        const Rows heads = ws.get("gated_attention.heads", T, static_cast<int64_t>(H) * E, dt);
-        const Rows g = gate >= 0 ? pr.columns(qkv_cols(), static_cast<int64_t>(H) * E) : Rows{};
-        kernels::head_gate(s, att, P, g, nullptr, heads, T, H, E, false, std::max(gate, 0), eps);
+        // Heads without a gate whose values fill the padded size are what the output projection reads, as they are.
+        const bool as_they_are = gate < 0 && P == E;
+        const Rows heads = as_they_are ? att : ws.get("gated_attention.heads", T, static_cast<int64_t>(H) * E, dt);
+        if (!as_they_are) {
+            const Rows g = gate >= 0 ? pr.columns(qkv_cols(), static_cast<int64_t>(H) * E) : Rows{};
+            kernels::head_gate(s, att, P, g, nullptr, heads, T, H, E, false, std::max(gate, 0), eps);
+        }
         ctx.tap("attention", heads);
         kernels::linear(ctx.runtime, &ws, heads, out.weight, nullptr, y, T, kernels::kNone, residual);
     }

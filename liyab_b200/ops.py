@@ -622,6 +622,8 @@ for _name, _args in {
     "lb_gated_act": [_i, _p, _l, _p, _l, _i, _i, _i, _p],
     "lb_matrix_memory": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _f, _f, _f, _i, _p],
     "lb_matrix_memory_pieces": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _i, _f, _f, _f, _p, _p],
+    "lb_matrix_memory_shared": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _f, _f, _f, _i, _i, _p],
+    "lb_matrix_memory_pieces_shared": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _i, _f, _f, _f, _p, _i, _p],
     "lb_router_topk": [_i, _p, _l, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "lb_expert_plan": [_p, _i, _i, _p, _p, _p, _p],
     "lb_expert_product": [_i, _i, _p, _l, _p, _l, _p, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _p],
@@ -688,22 +690,25 @@ def memory_slot_floats(n_head: int, dim: int, vdim: int, value_tile: int) -> int
 
 def matrix_memory(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, zi_off: Optional[int], zf_off: Optional[int], decay: Optional[torch.Tensor],
                   freq: Optional[torch.Tensor], rot_dims: int, positions: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
-                  out: torch.Tensor, n_head: int, dim: int, vdim: int, value_tile: int, q_scale: float, k_scale: float, cap: float, chunked: bool) -> torch.Tensor:
+                  out: torch.Tensor, n_head: int, dim: int, vdim: int, value_tile: int, q_scale: float, k_scale: float, cap: float, chunked: bool,
+                  qk_share: int = 1) -> torch.Tensor:
     """The matrix memories of csrc/matrix_memory.cu over the float rows `proj` whose columns hold q, k, v (and the gates' pre-activations) at the
-    given offsets; state [slots, memory_slot_floats(..)] float32."""
+    given offsets; state [slots, memory_slot_floats(..)] float32.  Without `decay` and without `zi_off` the column `zf_off` holds the log of the
+    factor a token and head; `qk_share` heads in a row read one query and key."""
     base = _dev(proj, "proj", torch.float32)
     at = lambda off: None if off is None else base + 4 * off
-    check(lib().lb_matrix_memory(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
+    check(lib().lb_matrix_memory_shared(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
                                  _opt(freq, "freq", torch.float32), rot_dims, _dev(positions, "positions", torch.int32), _dev(q_start, "q_start", torch.int32),
                                  _dev(slots, "slots", torch.int32), _dev(state, "state", torch.float32), state.stride(0), _dev(out, "out", torch.float32),
                                  out.stride(0), q_start.numel() - 1, n_head, dim, vdim, value_tile, float(q_scale), float(k_scale), float(cap), int(chunked),
-                                 stream_ptr()), "matrix_memory")
+                                 int(qk_share), stream_ptr()), "matrix_memory")
     return out
 
 
 def matrix_memory_pieces(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, zi_off: Optional[int], zf_off: Optional[int], decay: Optional[torch.Tensor],
                          freq: Optional[torch.Tensor], rot_dims: int, positions: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
-                         out: torch.Tensor, n_head: int, dim: int, vdim: int, value_tile: int, q_scale: float, k_scale: float, cap: float) -> torch.Tensor:
+                         out: torch.Tensor, n_head: int, dim: int, vdim: int, value_tile: int, q_scale: float, k_scale: float, cap: float,
+                         qk_share: int = 1) -> torch.Tensor:
     """matrix_memory in its form for long portions: every piece of 32 rows a block of its own (three launches)."""
     base = _dev(proj, "proj", torch.float32)
     at = lambda off: None if off is None else base + 4 * off
@@ -711,11 +716,11 @@ def matrix_memory_pieces(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
     fn = lib().lb_matrix_memory_pieces_floats
     fn.argtypes, fn.restype = [_i] * 6, _c.c_int64
     scratch = torch.empty(int(fn(T, S, n_head, dim, vdim, value_tile)), dtype=torch.float32, device=proj.device)
-    check(lib().lb_matrix_memory_pieces(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
+    check(lib().lb_matrix_memory_pieces_shared(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
                                         _opt(freq, "freq", torch.float32), rot_dims, _dev(positions, "positions", torch.int32),
                                         _dev(q_start, "q_start", torch.int32), _dev(slots, "slots", torch.int32), _dev(state, "state", torch.float32),
                                         state.stride(0), _dev(out, "out", torch.float32), out.stride(0), T, S, n_head, dim, vdim, value_tile, float(q_scale),
-                                        float(k_scale), float(cap), _dev(scratch, "scratch"), stream_ptr()), "matrix_memory_pieces")
+                                        float(k_scale), float(cap), _dev(scratch, "scratch"), int(qk_share), stream_ptr()), "matrix_memory_pieces")
     return out
 
 
@@ -758,6 +763,7 @@ for _name, _args in {
     "lb_gated_group_norm": [_i, _p, _l, _p, _l, _p, _i, _p, _l, _p, _p, _l, _i, _i, _i, _f, _p],
     "lb_gated_act_kind": [_i, _p, _l, _p, _l, _i, _i, _i, _f, _f, _p],
     "lb_router_topk_biased": [_i, _p, _l, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "lb_ssm_prepare": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _l, _p, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _i, _p],
 }.items():
     _SIGNATURES[_name] = _args
 
@@ -805,3 +811,17 @@ def router_topk(h: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tens
                                       _dev(ids, "ids"), _dev(weights, "weights"), T, router.shape[0], width, top, int(softmax), int(renormalise), stream_ptr()),
           "router_topk")
     return ids, weights
+
+
+def ssm_prepare(proj: torch.Tensor, xbc_off: int, dt_off: int, taps: torch.Tensor, tap_bias: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
+                a_log: torch.Tensor, state: torch.Tensor, tok_seq: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+                n_head: int, vdim: int, group_values: int, decode_only: bool) -> torch.Tensor:
+    """The rows a state space's recurrence reads (csrc/state_space.cu) from the float rows `proj`: the channels at `xbc_off` through their causal
+    convolution (`taps` [channels, K], the last K - 1 inputs of every request in `state` [slots, (K - 1) x channels]) and SiLU, the steps at `dt_off`
+    through softplus; out [T, 2 x n_head x vdim + group_values + n_head].  `decode_only`: every request brings one row."""
+    check(lib().lb_ssm_prepare(_dev(proj, "proj", torch.float32), proj.stride(0), xbc_off, dt_off, _dev(taps, "taps", torch.float32),
+                               _opt(tap_bias, "tap_bias", torch.float32), _opt(dt_bias, "dt_bias", torch.float32), _dev(a_log, "a_log", torch.float32),
+                               _dev(state, "state", torch.float32), state.stride(0), _dev(tok_seq, "tok_seq", torch.int32),
+                               _dev(q_start, "q_start", torch.int32), _dev(slots, "slots", torch.int32), _dev(out, "out", torch.float32), out.stride(0),
+                               proj.shape[0], q_start.numel() - 1, n_head, vdim, group_values, taps.shape[1], int(decode_only), stream_ptr()), "ssm_prepare")
+    return out

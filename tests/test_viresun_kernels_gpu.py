@@ -1,6 +1,7 @@
 """The kernels that came with Viresun, each by itself against a float64 statement written here: the penalty by distance in every
 attention kernel (32-bit, scalar decode with split keys, mma.sync prefill, tcgen05 prefill), the sinusoid of the position with the
-norm behind it, the gated norm in groups with a skip, the gates with a cap, and the router with a bias."""
+norm behind it, the gated norm in groups with a skip, the gates with a cap, the router with a bias, the convolution and step of the
+state space with its state across cuts, and the recurrence with a factor a token and keys shared by a group's heads in its three forms."""
 from __future__ import annotations
 
 import math
@@ -215,3 +216,113 @@ def test_router_with_a_bias(dev, dtype, experts, top, width):
     if experts > top:
         without = torch.argsort(-(z - bias.double()[None, :]), dim=1, stable=True)[:, :top]
         assert not torch.equal(without, order), "the bias does not show"
+
+
+def _t(a, dev, dtype=torch.float32):
+    return torch.tensor(np.ascontiguousarray(a), dtype=dtype, device=dev)
+
+
+@pytest.mark.parametrize("H,E,G,N,K,biases", [(4, 8, 2, 6, 4, True), (3, 5, 1, 7, 3, True), (2, 16, 2, 8, 1, False), (6, 4, 3, 2, 5, True),
+                                              (1, 1, 1, 1, 2, False), (8, 32, 2, 64, 4, True), (4, 12, 4, 10, 2, True)])
+def test_convolution_step_and_the_rows_of_the_recurrence(dev, H, E, G, N, K, biases):
+    """Three requests of unequal length in steps cut anywhere (portions, then single tokens in steps of their own), through scrambled state
+    slots: the convolution over the last K inputs with zeros before a sequence's start, SiLU, softplus of the step, and the rows
+    [x | B | C | dt x | -exp(A) dt], against the same made from each whole sequence in float64.  Sizes with channel counts that are and are not
+    multiples of four, and K = 4 beside other K."""
+    from liyab_b200 import ops
+    rng = np.random.default_rng(100 * H + K)
+    inner, GN2 = H * E, 2 * G * N
+    channels = inner + GN2
+    cols = inner + channels + H                     # [z | x B C | dt]
+    lens = [23, 9, 1]
+    cuts = [[5, 6, 19, 20, 21, 22, 23], [2, 9], [1]]
+    seqs = [rng.normal(0, 1.0, size=(n, cols)) for n in lens]
+    taps, tap_bias = rng.normal(0, K ** -0.5, size=(channels, K)), rng.normal(0, 0.3, size=channels) if biases else None
+    dt_bias, a_log = (rng.normal(-1.0, 0.8, size=H) if biases else None), rng.normal(-1.0, 1.0, size=H)
+
+    def whole(u):
+        xbc = u[:, inner:inner + channels]
+        padded = np.concatenate([np.zeros((K - 1, channels)), xbc])
+        conv = sum(padded[j:j + len(u)] * taps[:, j] for j in range(K)) + (tap_bias if biases else 0.0)
+        act = conv / (1.0 + np.exp(-conv))
+        dt = np.logaddexp(0.0, u[:, inner + channels:] + (dt_bias if biases else 0.0))
+        return np.concatenate([act, act[:, :inner] * np.repeat(dt, E, axis=1), -np.exp(a_log) * dt], axis=1)
+
+    want = [whole(u) for u in seqs]
+    slots = [2, 0, 3]
+    state = torch.zeros(4, max(1, (K - 1) * channels), dtype=torch.float32, device=dev)
+    at = [0, 0, 0]
+    for step in range(max(len(c) for c in cuts)):
+        live = [r for r in range(3) if step < len(cuts[r])]
+        parts = [seqs[r][at[r]:cuts[r][step]] for r in live]
+        q_start = np.concatenate([[0], np.cumsum([len(p) for p in parts])]).astype(np.int32)
+        tok_seq = np.concatenate([np.full(len(p), i) for i, p in enumerate(parts)]).astype(np.int32)
+        proj = _t(np.concatenate(parts), dev)
+        out = torch.full((proj.shape[0], 2 * inner + GN2 + H), float("nan"), dtype=torch.float32, device=dev)
+        ops.ssm_prepare(proj, inner, inner + channels, _t(taps, dev), _t(tap_bias, dev) if biases else None, _t(dt_bias, dev) if biases else None,
+                        _t(a_log, dev), state, _t(tok_seq, dev, torch.int32), _t(q_start, dev, torch.int32),
+                        _t(np.array([slots[r] for r in live]), dev, torch.int32), out, H, E, GN2, all(len(p) == 1 for p in parts))
+        ref = np.concatenate([want[r][at[r]:cuts[r][step]] for r in live])
+        err = np.abs(out.double().cpu().numpy() - ref).max() / np.abs(ref).max()
+        assert err < 2e-6, f"step {step}: {err:.2e}"
+        for r in live:
+            at[r] = cuts[r][step]
+    assert float(state[1].abs().max()) == 0.0                  # the slot no request used
+    if K > 1:                                                   # a request's state is its last K - 1 inputs, oldest first
+        last = np.concatenate([np.zeros((K - 1, channels)), seqs[0][:, inner:inner + channels]])[-(K - 1):]
+        assert np.abs(state[2].double().cpu().numpy().reshape(K - 1, channels) - last).max() < 1e-6
+
+
+@pytest.mark.parametrize("H,G,N,E,tile", [(4, 2, 16, 24, 24), (6, 1, 10, 70, 24), (2, 2, 64, 64, 32), (3, 3, 6, 5, 5), (8, 2, 128, 64, 32), (1, 1, 1, 1, 1)])
+def test_recurrence_with_a_factor_a_token_and_shared_keys(dev, H, G, N, E, tile):
+    """S_t = exp(f_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t with f <= 0 a number a token and head, heads of a group reading one key and query
+    row: three requests in steps cut anywhere, every step row by row, in pieces and with a block per piece from the same state, against
+    the recurrence in float64.  One head forgets almost nothing, one almost everything."""
+    from liyab_b200 import ops
+    rng = np.random.default_rng(11 * H + N)
+    lens, cuts = [150, 33, 1], [[40, 41, 150], [2, 33], [1]]
+    share = H // G
+    cols = 2 * G * N + H * E + H                    # [q | k | v | f]
+    rows = []
+    for n in lens:
+        x = rng.normal(0, 1.0, size=(n, cols))
+        x[:, -H:] = -np.abs(rng.normal(0, 0.5, size=(n, H)))
+        x[:, -H] *= 1e-3
+        if H > 1:
+            x[:, -1] -= 6.0
+        rows.append(x)
+    floats = ops.memory_slot_floats(H, N, E, tile)
+    modes = (False, True, "pieces")
+    states = {m: torch.zeros(4, floats, dtype=torch.float32, device=dev) for m in modes}
+    S = {(r, h): np.zeros((N, E)) for r in range(3) for h in range(H)}
+    slots, at = [2, 0, 3], [0, 0, 0]
+    for step in range(3):
+        live = [r for r in range(3) if step < len(cuts[r])]
+        parts = [rows[r][at[r]:cuts[r][step]] for r in live]
+        q_start = np.concatenate([[0], np.cumsum([len(p) for p in parts])]).astype(np.int32)
+        pos = np.concatenate([np.arange(at[r], cuts[r][step]) for r in live]).astype(np.int32)
+        want = np.zeros((int(q_start[-1]), H * E))
+        for i, r in enumerate(live):
+            for h in range(H):
+                g = h // share
+                for t, x in enumerate(parts[i]):
+                    q, k = x[g * N:(g + 1) * N], x[G * N + g * N:G * N + (g + 1) * N]
+                    v = x[2 * G * N + h * E:2 * G * N + (h + 1) * E]
+                    S[(r, h)] = math.exp(x[2 * G * N + H * E + h]) * S[(r, h)] + np.outer(k, v)
+                    want[q_start[i] + t, h * E:(h + 1) * E] = S[(r, h)].T @ q
+        proj = _t(np.concatenate(parts), dev)
+        for mode in modes:
+            out = torch.full((proj.shape[0], H * E), float("nan"), dtype=torch.float32, device=dev)
+            args = (proj, 0, G * N, 2 * G * N, None, 2 * G * N + H * E, None, None, 0, _t(pos, dev, torch.int32), _t(q_start, dev, torch.int32),
+                    _t(np.array([slots[r] for r in live]), dev, torch.int32), states[mode], out, H, N, E, tile, 1.0, 1.0, 0.0)
+            if mode == "pieces":
+                ops.matrix_memory_pieces(*args, qk_share=share)
+            else:
+                ops.matrix_memory(*args, mode, qk_share=share)
+            err = np.abs(out.double().cpu().numpy() - want).max() / max(np.abs(want).max(), 1e-30)
+            assert err < 5e-5, f"step {step}, {mode}: {err:.2e}"
+        for r in live:
+            at[r] = cuts[r][step]
+    for other in (True, "pieces"):
+        assert float((states[False] - states[other]).abs().max()) <= 1e-3 * float(states[False].abs().max())
+    assert float(states[False][1].abs().max()) == 0.0
