@@ -405,6 +405,78 @@ bool mma_takes(const ProductArgs& p) {
     return p.K % 8 == 0 && p.lda % 8 == 0 && p.expert_stride % 8 == 0 && ((uintptr_t)p.a & 15) == 0 && ((uintptr_t)p.w & 15) == 0;
 }
 
+// ---------------------------------------------------------------- the same products for a few pairs (bfloat16)
+// A decode step brings a pair or two an expert: a 64-row tile would be one row of work behind a long loop over K.  Here a block takes
+// one pair and `features` of its expert's output features; the pair's input row waits in shared memory, a warp makes a feature (both
+// matrices' where GATED) with K split over its lanes in 16-byte loads, several in flight, and the lanes meet by shuffles.  So a pair
+// streams its expert's matrices once with every SM taking part.  Sums are 32-bit in a fixed order; alignment as the tensor-core form's.
+template <bool GATED>
+__global__ void __launch_bounds__(128) expert_product_rows_kernel(ProductArgs p, int features) {
+    using B16 = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char rows_smem[];
+    uint4* a_s = reinterpret_cast<uint4*>(rows_smem);          // the input row, eight values an entry
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // The expert whose rows hold r: the last e with offsets[e] <= r.
+    int lo = 0, hi = p.E - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (p.offsets[mid] <= r) lo = mid; else hi = mid - 1;
+    }
+    const int e = lo, pair = p.pair_at[r];
+    const B16* a_row = static_cast<const B16*>(p.a) + (size_t)(GATED ? pair / p.top : r) * p.lda;
+    const int k8 = p.K / 8;
+    for (int i = threadIdx.x; i < k8; i += blockDim.x) a_s[i] = reinterpret_cast<const uint4*>(a_row)[i];
+    __syncthreads();
+    const float scale = GATED && p.weights != nullptr ? p.weights[pair] : 1.0f;
+    const B16* W = static_cast<const B16*>(p.w) + (size_t)e * p.expert_stride;
+    auto dot8 = [](const uint4& w, const uint4& a, float acc) {
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&w);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 wf = __bfloat1622float2(wp[j]), af = __bfloat1622float2(ap[j]);
+            acc = fmaf(wf.x, af.x, acc);
+            acc = fmaf(wf.y, af.y, acc);
+        }
+        return acc;
+    };
+    const int n_end = min(p.N, (int)(blockIdx.y + 1) * features);
+    for (int n = blockIdx.y * features + warp; n < n_end; n += 4) {
+        const uint4* w1 = reinterpret_cast<const uint4*>(W + (size_t)n * p.K);
+        const uint4* w2 = reinterpret_cast<const uint4*>(W + (size_t)(p.N + n) * p.K);
+        float acc = 0.0f, acc2 = 0.0f;
+#pragma unroll 4
+        for (int i = lane; i < k8; i += 32) {
+            const uint4 a = a_s[i];
+            acc = dot8(__ldg(w1 + i), a, acc);
+            if (GATED) acc2 = dot8(__ldg(w2 + i), a, acc2);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (GATED) acc2 += __shfl_xor_sync(0xffffffffu, acc2, o);
+        }
+        if (lane == 0) {
+            if (GATED) static_cast<B16*>(p.out)[(size_t)r * p.ldo + n] = __float2bfloat16_rn(lb_gated_pair(scale * acc, scale * acc2, p.act, p.alpha, p.limit));
+            else static_cast<float*>(p.out)[(size_t)r * p.ldo + n] = acc;
+        }
+    }
+}
+
+constexpr int kFewPairs = 64;
+
+template <bool GATED>
+int launch_product_rows(const ProductArgs& p, int n_pairs, cudaStream_t s) {
+    // About four blocks an SM, a block at least a feature a warp.
+    int features = (int)(((long)n_pairs * p.N + 591) / 592);
+    features = max(4, min(64, (features + 3) / 4 * 4));
+    const dim3 grid((unsigned)n_pairs, (unsigned)((p.N + features - 1) / features)), block(128);
+    LB_CHECK_CUDA(lb_launch_overlapped(expert_product_rows_kernel<GATED>, grid, block, (size_t)p.K * 2, s, p, features));
+    return LB_OK;
+}
+
 __global__ void expert_combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ place,
                                       int n_rows, int width, int top, const float* __restrict__ weights) {
     lb_wait_for_predecessor();
@@ -489,6 +561,8 @@ extern "C" int lb_expert_product_kind(int dtype, int gated, const void* a, int64
     ProductArgs p{a, lda, w, expert_stride, offsets, pair_at, weights, out, ldo, n_experts, n, k, top, act, alpha, limit};
     auto s = static_cast<cudaStream_t>(stream);
     if (dtype == LB_F32) return gated ? launch_product<float, true>(p, n_pairs, s) : launch_product<float, false>(p, n_pairs, s);
+    if (dtype == LB_BF16 && mma_takes(p) && !lb_expert_product_plain_only && n_pairs <= kFewPairs && (size_t)k * 2 <= 48 * 1024)
+        return gated ? launch_product_rows<true>(p, n_pairs, s) : launch_product_rows<false>(p, n_pairs, s);
     if (dtype == LB_BF16 && mma_takes(p) && !lb_expert_product_plain_only)
         return gated ? launch_product_mma<true>(p, n_pairs, s) : launch_product_mma<false>(p, n_pairs, s);
     if (dtype == LB_BF16) return gated ? launch_product<__nv_bfloat16, true>(p, n_pairs, s) : launch_product<__nv_bfloat16, false>(p, n_pairs, s);

@@ -191,10 +191,11 @@ def test_matrix_memories_row_by_row_and_in_pieces(gated, H, D, E, tile):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,E,top,width,inner", [(70, 6, 2, 96, 24), (3, 4, 1, 64, 16), (300, 16, 3, 128, 72), (40, 3, 3, 100, 10), (1, 1, 1, 8, 8)])
+@pytest.mark.parametrize("T,E,top,width,inner", [(70, 6, 2, 96, 24), (3, 4, 1, 64, 16), (300, 16, 3, 128, 72), (40, 3, 3, 100, 10), (1, 1, 1, 8, 8),
+                                                 (20, 5, 3, 128, 40), (9, 16, 2, 256, 72), (32, 2, 2, 64, 264)])
 def test_routed_experts(dtype, T, E, top, width, inner):
-    """Router, plan, both products and the sum against the plain statement; in bfloat16 the tensor-core products against the ones on the 32-bit
-    units as well.  The router's matrix is large, so that the experts are chosen by clear margins in either type."""
+    """Router, plan, both products and the sum against the plain statement; in bfloat16 the tensor-core products (and, for up to 64 pairs, the
+    products a pair at a time) against the ones on the 32-bit units as well.  The router's matrix is large, so that the experts are chosen by clear margins in either type."""
     import torch
     from liyab_b200 import ops
     dt = getattr(torch, dtype)
