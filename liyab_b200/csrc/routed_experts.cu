@@ -406,62 +406,85 @@ bool mma_takes(const ProductArgs& p) {
 }
 
 // ---------------------------------------------------------------- the same products for a few pairs (bfloat16)
-// A decode step brings a pair or two an expert: a 64-row tile would be one row of work behind a long loop over K.  Here a block takes
-// one pair and `features` of its expert's output features; the pair's input row waits in shared memory, a warp makes a feature (both
-// matrices' where GATED) with K split over its lanes in 16-byte loads, several in flight, and the lanes meet by shuffles.  So a pair
-// streams its expert's matrices once with every SM taking part.  Sums are 32-bit in a fixed order; alignment as the tensor-core form's.
+// A decode step brings a pair or two an expert: a 64-row tile would be one row of work behind a long loop over K.  Here a warp takes
+// one pair and F of its expert's output features (both matrices' where GATED), K split over its lanes in 16-byte loads.  Nothing
+// waits on anything it need not: the expert of a pair is found by one round of loads (every lane an offset, a ballot), the input row
+// is read by the lanes themselves, and 1,024 values of K of every row a warp reads travel together (cp.async, 20 pieces of 16 bytes a
+// lane in flight, whatever the compiler makes of the loop), so a launch is two round trips to memory and the stream of the experts'
+// matrices, with every SM taking part.  Sums are 32-bit in a fixed order; alignment as the tensor-core form's.
 template <bool GATED>
-__global__ void __launch_bounds__(128) expert_product_rows_kernel(ProductArgs p, int features) {
+__global__ void __launch_bounds__(128) expert_product_rows_kernel(ProductArgs p) {
     using B16 = __nv_bfloat16;
-    extern __shared__ __align__(16) unsigned char rows_smem[];
-    uint4* a_s = reinterpret_cast<uint4*>(rows_smem);          // the input row, eight values an entry
+    constexpr int F = GATED ? 2 : 4, kAhead = 4;
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // The expert whose rows hold r: the last e with offsets[e] <= r.
-    int lo = 0, hi = p.E - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (p.offsets[mid] <= r) lo = mid; else hi = mid - 1;
+    const int n0 = (blockIdx.y * 4 + warp) * F;
+    if (n0 >= p.N) return;
+    // The expert whose rows hold r: as many experts after the first start at or before r.
+    int e = 0;
+    for (int base = 1; base < p.E; base += 32) {
+        const bool at_or_before = base + lane < p.E && p.offsets[base + lane] <= r;
+        e += __popc(__ballot_sync(0xffffffffu, at_or_before));
     }
-    const int e = lo, pair = p.pair_at[r];
-    const B16* a_row = static_cast<const B16*>(p.a) + (size_t)(GATED ? pair / p.top : r) * p.lda;
-    const int k8 = p.K / 8;
-    for (int i = threadIdx.x; i < k8; i += blockDim.x) a_s[i] = reinterpret_cast<const uint4*>(a_row)[i];
-    __syncthreads();
-    const float scale = GATED && p.weights != nullptr ? p.weights[pair] : 1.0f;
+    const int pair = p.pair_at[r];
+    const uint4* a_row = reinterpret_cast<const uint4*>(static_cast<const B16*>(p.a) + (size_t)(GATED ? pair / p.top : r) * p.lda);
     const B16* W = static_cast<const B16*>(p.w) + (size_t)e * p.expert_stride;
-    auto dot8 = [](const uint4& w, const uint4& a, float acc) {
-        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&w);
-        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const int k8 = p.K / 8;
+    const uint4* w[GATED ? 2 * F : F];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 wf = __bfloat1622float2(wp[j]), af = __bfloat1622float2(ap[j]);
-            acc = fmaf(wf.x, af.x, acc);
-            acc = fmaf(wf.y, af.y, acc);
+    for (int f = 0; f < F; ++f) {
+        const int n = min(n0 + f, p.N - 1);                   // past the last feature: the last one again, not stored
+        w[f] = reinterpret_cast<const uint4*>(W + (size_t)n * p.K);
+        if (GATED) w[F + f] = reinterpret_cast<const uint4*>(W + (size_t)(p.N + n) * p.K);
+    }
+    constexpr int M = GATED ? 2 * F : F;
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+    auto dot8 = [](const uint4& wv, const uint4& av, float sum) {
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 wf = __bfloat1622float2(wp[q]), af = __bfloat1622float2(ap[q]);
+            sum = fmaf(wf.x, af.x, sum);
+            sum = fmaf(wf.y, af.y, sum);
         }
-        return acc;
+        return sum;
     };
-    const int n_end = min(p.N, (int)(blockIdx.y + 1) * features);
-    for (int n = blockIdx.y * features + warp; n < n_end; n += 4) {
-        const uint4* w1 = reinterpret_cast<const uint4*>(W + (size_t)n * p.K);
-        const uint4* w2 = reinterpret_cast<const uint4*>(W + (size_t)(p.N + n) * p.K);
-        float acc = 0.0f, acc2 = 0.0f;
-#pragma unroll 4
-        for (int i = lane; i < k8; i += 32) {
-            const uint4 a = a_s[i];
-            acc = dot8(__ldg(w1 + i), a, acc);
-            if (GATED) acc2 = dot8(__ldg(w2 + i), a, acc2);
-        }
+    // Every lane copies its own 16-byte pieces into places of its own and reads them back after its own wait: no barrier.
+    __shared__ __align__(16) uint4 ahead[4][kAhead][M + 1][32];
+    for (int i0 = lane; i0 < k8; i0 += 32 * kAhead) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (GATED) acc2 += __shfl_xor_sync(0xffffffffu, acc2, o);
+        for (int s = 0; s < kAhead; ++s) {
+            const int i = i0 + 32 * s;
+            const bool in = i < k8;                           // past the end: zeros
+            cp_async16(&ahead[warp][s][M][lane], a_row + (in ? i : 0), in);
+#pragma unroll
+            for (int m = 0; m < M; ++m) cp_async16(&ahead[warp][s][m][lane], w[m] + (in ? i : 0), in);
         }
-        if (lane == 0) {
-            if (GATED) static_cast<B16*>(p.out)[(size_t)r * p.ldo + n] = __float2bfloat16_rn(lb_gated_pair(scale * acc, scale * acc2, p.act, p.alpha, p.limit));
-            else static_cast<float*>(p.out)[(size_t)r * p.ldo + n] = acc;
+        cp_async_commit();
+        cp_async_wait<0>();
+#pragma unroll
+        for (int s = 0; s < kAhead; ++s) {
+            const uint4 av = ahead[warp][s][M][lane];
+#pragma unroll
+            for (int m = 0; m < M; ++m) acc[m] = dot8(ahead[warp][s][m][lane], av, acc[m]);
         }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+    if (lane != 0) return;
+    const float scale = GATED && p.weights != nullptr ? p.weights[pair] : 1.0f;
+#pragma unroll
+    for (int f = 0; f < F; ++f) {
+        const int n = n0 + f;
+        if (n >= p.N) break;
+        if (GATED) static_cast<B16*>(p.out)[(size_t)r * p.ldo + n] = __float2bfloat16_rn(lb_gated_pair(scale * acc[f], scale * acc[F + f], p.act, p.alpha, p.limit));
+        else static_cast<float*>(p.out)[(size_t)r * p.ldo + n] = acc[f];
     }
 }
 
@@ -469,11 +492,9 @@ constexpr int kFewPairs = 64;
 
 template <bool GATED>
 int launch_product_rows(const ProductArgs& p, int n_pairs, cudaStream_t s) {
-    // About four blocks an SM, a block at least a feature a warp.
-    int features = (int)(((long)n_pairs * p.N + 591) / 592);
-    features = max(4, min(64, (features + 3) / 4 * 4));
+    const int features = 4 * (GATED ? 2 : 4);       // a block's four warps, F features each
     const dim3 grid((unsigned)n_pairs, (unsigned)((p.N + features - 1) / features)), block(128);
-    LB_CHECK_CUDA(lb_launch_overlapped(expert_product_rows_kernel<GATED>, grid, block, (size_t)p.K * 2, s, p, features));
+    LB_CHECK_CUDA(lb_launch_overlapped(expert_product_rows_kernel<GATED>, grid, block, 0, s, p));
     return LB_OK;
 }
 
@@ -561,7 +582,7 @@ extern "C" int lb_expert_product_kind(int dtype, int gated, const void* a, int64
     ProductArgs p{a, lda, w, expert_stride, offsets, pair_at, weights, out, ldo, n_experts, n, k, top, act, alpha, limit};
     auto s = static_cast<cudaStream_t>(stream);
     if (dtype == LB_F32) return gated ? launch_product<float, true>(p, n_pairs, s) : launch_product<float, false>(p, n_pairs, s);
-    if (dtype == LB_BF16 && mma_takes(p) && !lb_expert_product_plain_only && n_pairs <= kFewPairs && (size_t)k * 2 <= 48 * 1024)
+    if (dtype == LB_BF16 && mma_takes(p) && !lb_expert_product_plain_only && n_pairs <= kFewPairs)
         return gated ? launch_product_rows<true>(p, n_pairs, s) : launch_product_rows<false>(p, n_pairs, s);
     if (dtype == LB_BF16 && mma_takes(p) && !lb_expert_product_plain_only)
         return gated ? launch_product_mma<true>(p, n_pairs, s) : launch_product_mma<false>(p, n_pairs, s);
