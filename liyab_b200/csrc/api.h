@@ -417,6 +417,64 @@ int lb_ssm_prepare(const float* proj, int64_t ld, int xbc_off, int dt_off, const
 int lb_gated_group_norm(int out_dtype, const float* o, int64_t ldo, const float* skip, int64_t lds, const float* skip_gain, int head, const float* z,
                         int64_t ldz, const float* weight, void* out, int64_t ld_out, int n_rows, int width, int groups, float eps, void* stream);
 
+/* lb_paged_attention_generic_biased with a sink a head: `sink` [n_head] (or null); exp(sink[h]) joins the divisor of head h's softmax as it is
+ * (not scaled), with no key and no value. */
+int lb_paged_attention_generic_sink(int dtype, const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq, const int32_t* positions,
+                                    const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_tokens, int n_head,
+                                    int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance, const float* sink,
+                                    void* stream);
+
+/* What attention over latent rows may have besides its sizes.  sink [n_head]: exp(sink[h]) joins the divisor of head h's softmax (no key, no
+ * value, not scaled).  gate: one float a (token, head) at gate[t * ldg + h]; the head's result is multiplied by sigmoid of it.  interleaved:
+ * the rotation pairs value 2i with 2i + 1 instead of i with i + rot_dims / 2.  latent (lb_latent_prepare_ext): the rows [latent | rotated key],
+ * ldl floats apart, where they do not follow the queries in qd.  A null pointer to the struct means none of it. */
+typedef struct lb_latent_extras {
+    const float* sink;
+    const float* gate;
+    int64_t ldg;
+    int interleaved;
+    const float* latent;
+    int64_t ldl;
+} lb_latent_extras;
+int lb_latent_store_ext(int cache_dtype, const float* d, int64_t ldd, const float* gain, const float* freq, const int32_t* positions,
+                        const int32_t* slot_mapping, void* cache, int n_tokens, int rank, int rot, int rot_dims, float eps, const lb_latent_extras* extras,
+                        void* stream);
+int lb_rope_heads_ext(int q_dtype, int wide_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, void* wide, int64_t ldw,
+                      int n_tokens, int n_head, int dim, int rot, int rot_dims, int rank, int interleaved, void* stream);
+int lb_latent_prepare_ext(const float* qd, int64_t ldq, const void* uk, const float* gain, const float* freq, const int32_t* positions,
+                          const int32_t* slot_mapping, void* cache, void* wide, int64_t ldw, int n_tokens, int n_head, int dim, int rot, int rot_dims,
+                          int rank, float eps, const lb_latent_extras* extras, void* stream);
+/* Sink and gate act here where the keys were split (n_splits > 1); with one part only the gate does (the attention applied the sink). */
+int lb_latent_finish_ext(const float* attended, int64_t lda, const float* part_o, const float* part_ml, const void* uv, void* values, int64_t ldv,
+                         int n_tokens, int n_head, int rank, int vdim, int n_splits, const lb_latent_extras* extras, void* stream);
+int lb_latent_attention_ext(int cache_dtype, const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq, const int32_t* positions,
+                            const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens, int n_head, int rank, int rot,
+                            int page_size, float scale, int window, const lb_latent_extras* extras, void* stream);
+int lb_latent_attention_rows16_ext(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                   const int32_t* block_table, int table_stride, void* out, int64_t ldo, int n_tokens, int n_seq, int max_q_len,
+                                   int n_head, int rank, int rot, int page_size, float scale, int window, const lb_latent_extras* extras, void* stream);
+int lb_latent_attention_mma_ext(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                const int32_t* block_table, int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml, int n_tokens,
+                                int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window, int n_splits,
+                                int merge_parts, const lb_latent_extras* extras, void* stream);
+
+/* Queries, keys and values of a float projection on their way to attention (see rotary_rows.cu).  norm_mode 0 none, 1 every head over its
+ * root mean square (gains [dim]), 2 all of q and all of k each over one root mean square (gains [n_head * dim], [n_kv_head * dim]); then the
+ * first rot_dims values of every query and key head rotated (value i with i + rot_dims / 2, angle positions[t] * freq[i]).  Values: with
+ * v_first_in, v = (1 - lambda[0]) v + lambda[0] v_first_in[t]; with v_first_out the row's own values are left there (rows ldv floats apart,
+ * n_kv_head * vdim values).  Destinations as lb_qk_norm_store's. */
+int lb_qkv_rotary_store(int dtype, const float* proj, int64_t ld, int q_off, int k_off, int v_off, const float* q_weight, const float* k_weight,
+                        void* q_out, int64_t ldq, void* cache, const int32_t* slot_mapping, int n_tokens, int n_head, int n_kv_head, int dim, int vdim,
+                        int padded, int page_size, int norm_mode, float eps, const int32_t* positions, const float* freq, int rot_dims,
+                        const float* v_first_in, float* v_first_out, int64_t ldv, const float* lambda, void* stream);
+/* out[r, c] = o[r, c] / sqrt(mean(o[r, :]^2) + eps) * gain[c] * act(g[r, c]); gain and g may be null; act 0 sigmoid, 1 silu. */
+int lb_row_norm_gate(int out_dtype, const float* o, int64_t ldo, const float* g, int64_t ldg, const float* gain, void* out, int64_t ld_out, int n_rows,
+                     int width, int act, float eps, void* stream);
+/* x[r, c] = act(x[r, c]) for c < cols, in place; act 0 sigmoid, 1 silu, 2 GELU (tanh form), 3 relu. */
+int lb_activate_columns(float* x, int64_t ld, int n_rows, int cols, int act, void* stream);
+/* ids[r, j] = table[tokens[r], j] and weights[r, j] = 1 / top: a row's experts looked up by its token id (table int32 [vocab, top]). */
+int lb_router_table(const int32_t* tokens, const int32_t* table, int32_t* ids, float* weights, int n_rows, int top, int n_experts, int vocab, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

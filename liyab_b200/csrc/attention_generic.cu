@@ -99,7 +99,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
                                const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions,
                                const int32_t* __restrict__ block_table, int table_stride, T* __restrict__ out,
                                int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
-                               int page_size, float scale, int window, const float* __restrict__ distance) {
+                               int page_size, float scale, int window, const float* __restrict__ distance, const float* __restrict__ sink) {
     extern __shared__ float smem[];
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
@@ -180,9 +180,10 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
     __syncthreads();
     T* o_row = out + (size_t)t * out_stride + (size_t)h * head_dim;
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float top = -CUDART_INF_F;
+        // A head's sink joins the divisor as a state without values: maximum sink[h], sum 1.
+        float top = sink != nullptr ? sink[h] : -CUDART_INF_F;
         for (int w = 0; w < n_warps; ++w) top = fmaxf(top, merge[(size_t)w * (head_dim + 2)]);
-        float total = 0.0f, o = 0.0f;
+        float total = sink != nullptr ? expf(sink[h] - top) : 0.0f, o = 0.0f;
         for (int w = 0; w < n_warps; ++w) {
             const float* st = merge + (size_t)w * (head_dim + 2);
             const float f = expf(st[0] - top);      // exp(-inf) = 0 for a warp without keys
@@ -231,7 +232,7 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
                                const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions,
                                const int32_t* __restrict__ block_table, int table_stride, float* __restrict__ out,
                                int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
-                               int page_size, float scale, int window, const float* __restrict__ distance) {
+                               int page_size, float scale, int window, const float* __restrict__ distance, const float* __restrict__ sink) {
     extern __shared__ __align__(16) float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const int pair = blockIdx.x;
@@ -338,9 +339,10 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
     __syncthreads();
     float* o_row = out + (size_t)t * out_stride + (size_t)h * head_dim;
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float top = -CUDART_INF_F;
+        // A head's sink joins the divisor as a state without values: maximum sink[h], sum 1.
+        float top = sink != nullptr ? sink[h] : -CUDART_INF_F;
         for (int w = 0; w < n_warps; ++w) top = fmaxf(top, merge[(size_t)w * (head_dim + 2)]);
-        float total = 0.0f, o = 0.0f;
+        float total = sink != nullptr ? expf(sink[h] - top) : 0.0f, o = 0.0f;
         for (int w = 0; w < n_warps; ++w) {
             const float* st = merge + (size_t)w * (head_dim + 2);
             const float f = expf(st[0] - top);      // exp(-inf) = 0 for a warp without keys
@@ -368,7 +370,7 @@ int warps_for(int head_dim) {
 template <typename T>
 int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq, const int32_t* positions,
            const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_tokens, int n_head,
-           int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance, cudaStream_t s) {
+           int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance, const float* sink, cudaStream_t s) {
     const int warps = warps_for(head_dim);
     const size_t smem = (size_t)warps * (head_dim + kTile * (head_dim + 1) + kTile + head_dim + 2) * sizeof(float);
     static size_t configured = 0;   // largest dynamic shared memory asked for so far
@@ -390,14 +392,14 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* to
             }
             LB_CHECK_CUDA(lb_launch_overlapped(paged_attention_f32_few_kernel, dim3((unsigned)pairs), dim3(warps * 32), few, s, 
                 (const float*)q, q_stride, (const float*)cache, tok_seq, positions, block_table, table_stride, (float*)out, out_stride,
-                n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance));
+                n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance, sink));
             LB_CHECK_LAUNCH();
             return LB_OK;
         }
     }
     LB_CHECK_CUDA(lb_launch_overlapped(paged_attention_generic_kernel<T>, dim3((unsigned)pairs), dim3(warps * 32), smem, s, 
         (const T*)q, q_stride, (const T*)cache, tok_seq, positions, block_table, table_stride, (T*)out, out_stride,
-        n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance));
+        n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance, sink));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
@@ -417,6 +419,14 @@ extern "C" int lb_paged_attention_generic_biased(int dtype, const void* q, int64
                                                  const int32_t* positions, const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
                                                  int n_tokens, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window,
                                                  const float* distance, void* stream) {
+    return lb_paged_attention_generic_sink(dtype, q, q_stride, cache, tok_seq, positions, block_table, table_stride, out, out_stride, n_tokens, n_head,
+                                           n_kv_head, head_dim, page_size, scale, window, distance, nullptr, stream);
+}
+
+extern "C" int lb_paged_attention_generic_sink(int dtype, const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq,
+                                               const int32_t* positions, const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
+                                               int n_tokens, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window,
+                                               const float* distance, const float* sink, void* stream) {
     LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_kv_head > 0 && page_size > 0, "attention: bad sizes");
     LB_CHECK_ARG(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
     LB_CHECK_ARG(head_dim > 0 && head_dim <= kMaxHeadDim, "attention: head_dim %d is outside (0, %d]", head_dim,
@@ -425,9 +435,9 @@ extern "C" int lb_paged_attention_generic_biased(int dtype, const void* q, int64
     auto s = static_cast<cudaStream_t>(stream);
     if (dtype == LB_F32)
         return launch<float>(q, q_stride, cache, tok_seq, positions, block_table, table_stride, out, out_stride,
-                             n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance, s);
+                             n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance, sink, s);
     if (dtype == LB_BF16)
         return launch<__nv_bfloat16>(q, q_stride, cache, tok_seq, positions, block_table, table_stride, out,
-                                     out_stride, n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance, s);
+                                     out_stride, n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, distance, sink, s);
     return lb_fail(LB_ERR_INVALID_ARGUMENT, "attention: unknown dtype %d", dtype);
 }

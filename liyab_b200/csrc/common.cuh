@@ -36,6 +36,8 @@ enum lb_activation : int {
     // xIELU: z > 0 -> a z^2 + z/2, else b (exp(z) - 1 - z) + z/2 with a = softplus(p), b = 1/2 + softplus(q).  The two learned numbers
     // travel behind the bias: a product with this activation is given a bias of N + 2 floats, bias[N] = p and bias[N + 1] = q.
     LB_ACT_XIELU = 3,
+    // The square of relu: max(z, 0)^2.
+    LB_ACT_RELU2 = 4,
 };
 
 int lb_fail(int code, const char* fmt, ...);
@@ -182,6 +184,7 @@ __device__ __forceinline__ lb_act_pair lb_act_load(const float* bias, int N, int
 __device__ __forceinline__ float lb_activate(float x, int act) {
     if (act == LB_ACT_GELU_TANH) return lb_gelu_tanh(x);
     if (act == LB_ACT_GELU_ERF) return lb_gelu_erf(x);
+    if (act == LB_ACT_RELU2) return x > 0.0f ? x * x : 0.0f;
     return x;
 }
 

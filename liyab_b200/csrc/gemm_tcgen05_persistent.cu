@@ -204,6 +204,9 @@ __device__ __forceinline__ float activate(float x, const lb_act_pair& p) {
             return fmaf(p.a * pos, pos, fmaf(p.b, __expf(neg) - 1.0f - neg, 0.5f * x));
         }
         else return lb_xielu(x, p.a, p.b);
+    } else if constexpr (ACT == LB_ACT_RELU2) {
+        const float pos = fmaxf(x, 0.0f);
+        return pos * pos;
     } else {
         return x;
     }
@@ -794,6 +797,7 @@ static int launch_persistent(int out_dtype, const void* A, int64_t lda, const vo
         case LB_ACT_GELU_TANH: LB_GO(TO, LB_ACT_GELU_TANH, RES); break;     \
         case LB_ACT_GELU_ERF: LB_GO(TO, LB_ACT_GELU_ERF, RES); break;       \
         case LB_ACT_XIELU: LB_GO(TO, LB_ACT_XIELU, RES); break;             \
+        case LB_ACT_RELU2: LB_GO(TO, LB_ACT_RELU2, RES); break;             \
         default: return lb_fail(LB_ERR_INVALID_ARGUMENT, "gemm_persistent: unknown activation %d", act); \
     }
     if (pair) {

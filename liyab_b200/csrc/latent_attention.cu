@@ -19,6 +19,14 @@
 namespace {
 
 // The pair (u, v) = (x[i], x[i + half]) at angle a = position * freq[i] becomes (u cos a - v sin a, v cos a + u sin a).
+// Where pair i of a rotation over `rot_dims` values lies: (i, i + rot_dims / 2), or side by side (2i, 2i + 1) when `interleaved`.
+__device__ __forceinline__ int pair_lo(int i, int interleaved) { return interleaved ? 2 * i : i; }
+__device__ __forceinline__ int pair_hi(int i, int half, int interleaved) { return interleaved ? 2 * i + 1 : half + i; }
+// What multiplies a (token, head)'s result besides the softmax: sigmoid of the head's gate, where there is one.
+__device__ __forceinline__ float head_factor(const float* gate, int64_t ldg, int t, int h) {
+    return gate != nullptr ? 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h])) : 1.0f;
+}
+
 __device__ __forceinline__ void rotate_pair(float u, float v, int position, float freq, float* ru, float* rv) {
     float sn, cs;
     sincosf((float)position * freq, &sn, &cs);
@@ -29,7 +37,7 @@ __device__ __forceinline__ void rotate_pair(float u, float v, int position, floa
 template <typename T>
 __global__ void latent_store_kernel(const float* __restrict__ d, int64_t ldd, const float* __restrict__ gain, const float* __restrict__ freq,
                                     const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping, T* __restrict__ cache,
-                                    int rank, int rot, int rot_dims, float eps) {
+                                    int rank, int rot, int rot_dims, float eps, int interleaved) {
     __shared__ float scratch[33];
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
@@ -45,9 +53,10 @@ __global__ void latent_store_kernel(const float* __restrict__ d, int64_t ldd, co
     const int half = rot_dims / 2, p = positions[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float u, v;
-        rotate_pair(in[rank + i], in[rank + half + i], p, freq[i], &u, &v);
-        out[rank + i] = lb_from_float<T>(u);
-        out[rank + half + i] = lb_from_float<T>(v);
+        const int a = rank + pair_lo(i, interleaved), b = rank + pair_hi(i, half, interleaved);
+        rotate_pair(in[a], in[b], p, freq[i], &u, &v);
+        out[a] = lb_from_float<T>(u);
+        out[b] = lb_from_float<T>(v);
     }
     for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) out[rank + i] = lb_from_float<T>(in[rank + i]);
 }
@@ -55,7 +64,7 @@ __global__ void latent_store_kernel(const float* __restrict__ d, int64_t ldd, co
 // q: [T, H * (dim + rot)], head by head [dim | rot]; wide: [T, H * (rank + rot)] float, head by head [rank | rot].
 template <typename T, typename TW>
 __global__ void rope_heads_kernel(const T* __restrict__ q, int64_t ldq, const float* __restrict__ freq, const int32_t* __restrict__ positions,
-                                  TW* __restrict__ wide, int64_t ldw, int n_head, int dim, int rot, int rot_dims, int rank) {
+                                  TW* __restrict__ wide, int64_t ldw, int n_head, int dim, int rot, int rot_dims, int rank, int interleaved) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int t = blockIdx.x, p = positions[t], half = rot_dims / 2;
@@ -66,9 +75,10 @@ __global__ void rope_heads_kernel(const T* __restrict__ q, int64_t ldq, const fl
         TW* out = wide + (size_t)t * ldw + (size_t)h * (rank + rot) + rank;
         if (i < half) {
             float u, v;
-            rotate_pair(lb_to_float(in[i]), lb_to_float(in[half + i]), p, freq[i], &u, &v);
-            out[i] = lb_from_float<TW>(u);
-            out[half + i] = lb_from_float<TW>(v);
+            const int a = pair_lo(i, interleaved), b = pair_hi(i, half, interleaved);
+            rotate_pair(lb_to_float(in[a]), lb_to_float(in[b]), p, freq[i], &u, &v);
+            out[a] = lb_from_float<TW>(u);
+            out[b] = lb_from_float<TW>(v);
         } else {
             out[rot_dims + i - half] = lb_from_float<TW>(lb_to_float(in[rot_dims + i - half]));
         }
@@ -83,7 +93,7 @@ __global__ void __launch_bounds__(128)
 latent_prepare_kernel(const float* __restrict__ qd, int64_t ldq, const __nv_bfloat16* __restrict__ uk, const float* __restrict__ gain,
                       const float* __restrict__ freq, const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
                       __nv_bfloat16* __restrict__ cache, __nv_bfloat16* __restrict__ wide, int64_t ldw, int n_head, int dim, int rot, int rot_dims,
-                      int rank, float eps, int q_cols) {
+                      int rank, float eps, int q_cols, const float* __restrict__ latent, int64_t ldl, int interleaved) {
     extern __shared__ __align__(16) unsigned char prep_sm[];
     __nv_bfloat16* map = reinterpret_cast<__nv_bfloat16*>(prep_sm);                     // [dim][rank]
     float* qsm = reinterpret_cast<float*>(prep_sm + (((size_t)dim * rank * 2 + 15) & ~(size_t)15));     // the head's query [dim + rot]
@@ -100,7 +110,7 @@ latent_prepare_kernel(const float* __restrict__ qd, int64_t ldq, const __nv_bflo
     if (h == n_head) {
         const int slot = slot_mapping[t];
         if (slot < 0) return;
-        const float* in = qd + (size_t)t * ldq + q_cols;
+        const float* in = latent != nullptr ? latent + (size_t)t * ldl : qd + (size_t)t * ldq + q_cols;
         __nv_bfloat16* out = cache + (size_t)slot * (rank + rot);
         float ss = 0.0f;
         for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
@@ -108,9 +118,10 @@ latent_prepare_kernel(const float* __restrict__ qd, int64_t ldq, const __nv_bflo
         for (int i = threadIdx.x; i < rank; i += blockDim.x) out[i] = __float2bfloat16_rn(in[i] * inv * gain[i]);
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             float u, v;
-            rotate_pair(in[rank + i], in[rank + half + i], p, freq[i], &u, &v);
-            out[rank + i] = __float2bfloat16_rn(u);
-            out[rank + half + i] = __float2bfloat16_rn(v);
+            const int a = rank + pair_lo(i, interleaved), b = rank + pair_hi(i, half, interleaved);
+            rotate_pair(in[a], in[b], p, freq[i], &u, &v);
+            out[a] = __float2bfloat16_rn(u);
+            out[b] = __float2bfloat16_rn(v);
         }
         for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) out[rank + i] = __float2bfloat16_rn(in[rank + i]);
         return;
@@ -121,9 +132,10 @@ latent_prepare_kernel(const float* __restrict__ qd, int64_t ldq, const __nv_bflo
     __nv_bfloat16* out = wide + (size_t)t * ldw + (size_t)h * (rank + rot);
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float u, v;
-        rotate_pair(qsm[dim + i], qsm[dim + half + i], p, freq[i], &u, &v);
-        out[rank + i] = __float2bfloat16_rn(u);
-        out[rank + half + i] = __float2bfloat16_rn(v);
+        const int a = pair_lo(i, interleaved), b = pair_hi(i, half, interleaved);
+        rotate_pair(qsm[dim + a], qsm[dim + b], p, freq[i], &u, &v);
+        out[rank + a] = __float2bfloat16_rn(u);
+        out[rank + b] = __float2bfloat16_rn(v);
     }
     for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) out[rank + i] = __float2bfloat16_rn(qsm[dim + i]);
     for (int n = threadIdx.x; n < rank; n += blockDim.x) {
@@ -139,7 +151,7 @@ latent_prepare_kernel(const float* __restrict__ qd, int64_t ldq, const __nv_bflo
 __global__ void __launch_bounds__(128)
 latent_finish_kernel(const float* __restrict__ attended, int64_t lda, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                      const __nv_bfloat16* __restrict__ uv, __nv_bfloat16* __restrict__ values, int64_t ldv, int n_tokens, int n_head, int rank, int vdim,
-                     int n_splits) {
+                     int n_splits, const float* __restrict__ sink, const float* __restrict__ gate, int64_t ldg) {
     extern __shared__ float osm[];             // the attended latent [rank], then the parts' factors [n_splits]
     float* factor = osm + rank;
     lb_wait_for_predecessor();
@@ -166,9 +178,11 @@ latent_finish_kernel(const float* __restrict__ attended, int64_t lda, const floa
                 ms = ml.x;
                 ls = ml.y;
             }
-            const float m = lb_warp_max(ms);
+            // A head's sink joins the divisor as a part without values: maximum sink (in the parts' base-2 scale), sum 1.
+            const float sk = sink != nullptr ? sink[h] * 1.4426950408889634f : -CUDART_INF_F;
+            const float m = fmaxf(lb_warp_max(ms), sk);
             const float e = ms == -CUDART_INF_F ? 0.0f : exp2f(ms - m);
-            float l = 0.0f;
+            float l = sink != nullptr ? exp2f(sk - m) : 0.0f;
             for (int s = 0; s < n_splits; ++s) l += __shfl_sync(0xffffffffu, e * ls, s);
             if (lane < n_splits) factor[lane] = e / l;
         }
@@ -198,6 +212,7 @@ latent_finish_kernel(const float* __restrict__ attended, int64_t lda, const floa
         for (int d = threadIdx.x; d < rank; d += blockDim.x) osm[d] = attended[(size_t)t * lda + (size_t)h * rank + d];
     }
     __syncthreads();
+    const float times = head_factor(gate, ldg, t, h);
     const int pieces = rank / 8;
     // A warp's values in batches of eight; a batch's first pieces are all asked for before any is used.
     for (int v0 = warp; v0 < vdim; v0 += 32) {
@@ -225,7 +240,7 @@ latent_finish_kernel(const float* __restrict__ attended, int64_t lda, const floa
                 }
             }
             acc = lb_warp_sum(acc);
-            if (lane == 0) values[(size_t)t * ldv + (size_t)h * vdim + v] = __float2bfloat16_rn(acc);
+            if (lane == 0) values[(size_t)t * ldv + (size_t)h * vdim + v] = __float2bfloat16_rn(acc * times);
         }
     }
 }
@@ -296,7 +311,8 @@ template <typename T, int RPL>
 __global__ void __launch_bounds__(128)
 latent_attention_kernel(const float* __restrict__ wide, int64_t ldw, const T* __restrict__ cache, const int32_t* __restrict__ tok_seq,
                         const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride, float* __restrict__ out,
-                        int64_t ldo, int n_head, int rank, int rot, int page_size, float scale, int window) {
+                        int64_t ldo, int n_head, int rank, int rot, int page_size, float scale, int window, const float* __restrict__ sink,
+                        const float* __restrict__ gate, int64_t ldg) {
     extern __shared__ float sm[];
     const int D = rank + rot, DS = D | 1;                 // odd row stride: lanes reading one column of 32 rows hit 32 banks
     float* qs = sm;                                        // [4][D]
@@ -353,7 +369,14 @@ latent_attention_kernel(const float* __restrict__ wide, int64_t ldw, const T* __
         m = m_new;
     }
     if (!active) return;
-    const float inv = 1.0f / l;
+    // A head's sink adds exp(sink) to the divisor (no key, no value); the head's gate multiplies the result.
+    if (sink != nullptr) {
+        const float top = fmaxf(m, sink[h]), f = expf(m - top);
+        l = l * f + expf(sink[h] - top);
+#pragma unroll
+        for (int r = 0; r < RPL; ++r) o[r] *= f;
+    }
+    const float inv = head_factor(gate, ldg, t, h) / l;
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
         const int d = lane + 32 * r;
@@ -364,23 +387,23 @@ latent_attention_kernel(const float* __restrict__ wide, int64_t ldw, const T* __
 template <typename T, int RPL>
 int launch_latent_attention(const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq, const int32_t* positions,
                             const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens, int n_head, int rank, int rot,
-                            int page_size, float scale, int window, cudaStream_t s) {
+                            int page_size, float scale, int window, const float* sink, const float* gate, int64_t ldg, cudaStream_t s) {
     const int D = rank + rot;
     const size_t smem = ((size_t)kHeadsPerBlock * D + 32 * (size_t)(D | 1)) * sizeof(float);
     if (smem > 220 * 1024) return lb_fail(LB_ERR_UNSUPPORTED, "latent attention: cache rows of %d values do not fit a block", D);
     if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_kernel<T, RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid(n_tokens, (n_head + kHeadsPerBlock - 1) / kHeadsPerBlock);
     LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_kernel<T, RPL>, grid, dim3(128), smem, s, wide, ldw, (const T*)cache, tok_seq, positions,
-                                       block_table, table_stride, out, ldo, n_head, rank, rot, page_size, scale, window));
+                                       block_table, table_stride, out, ldo, n_head, rank, rot, page_size, scale, window, sink, gate, ldg));
     return LB_OK;
 }
 
 template <typename T>
 int pick_latent_attention(const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq, const int32_t* positions,
                           const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens, int n_head, int rank, int rot,
-                          int page_size, float scale, int window, cudaStream_t s) {
+                          int page_size, float scale, int window, const float* sink, const float* gate, int64_t ldg, cudaStream_t s) {
 #define LB_LATENT(RPL) launch_latent_attention<T, RPL>(wide, ldw, cache, tok_seq, positions, block_table, table_stride, out, ldo, n_tokens, n_head, \
-                                                       rank, rot, page_size, scale, window, s)
+                                                       rank, rot, page_size, scale, window, sink, gate, ldg, s)
     if (rank <= 128) return LB_LATENT(4);
     if (rank <= 256) return LB_LATENT(8);
     if (rank <= 512) return LB_LATENT(16);
@@ -402,6 +425,13 @@ int launch_head_matmul(const void* A, int64_t lda, int64_t a_head, const void* B
 
 extern "C" int lb_latent_store(int cache_dtype, const float* d, int64_t ldd, const float* gain, const float* freq, const int32_t* positions,
                                const int32_t* slot_mapping, void* cache, int n_tokens, int rank, int rot, int rot_dims, float eps, void* stream) {
+    return lb_latent_store_ext(cache_dtype, d, ldd, gain, freq, positions, slot_mapping, cache, n_tokens, rank, rot, rot_dims, eps, nullptr, stream);
+}
+
+extern "C" int lb_latent_store_ext(int cache_dtype, const float* d, int64_t ldd, const float* gain, const float* freq, const int32_t* positions,
+                                   const int32_t* slot_mapping, void* cache, int n_tokens, int rank, int rot, int rot_dims, float eps,
+                                   const lb_latent_extras* extras, void* stream) {
+    const int interleaved = extras != nullptr ? extras->interleaved : 0;
     LB_CHECK_ARG(n_tokens >= 0 && rank > 0 && rot >= 0 && rot_dims >= 0 && rot_dims <= rot && rot_dims % 2 == 0,
                  "latent store: bad sizes rank=%d rot=%d rotated=%d", rank, rot, rot_dims);
     if (n_tokens == 0) return LB_OK;
@@ -409,10 +439,10 @@ extern "C" int lb_latent_store(int cache_dtype, const float* d, int64_t ldd, con
     const int threads = rank >= 512 ? 256 : 128;
     if (cache_dtype == LB_F32)
         LB_CHECK_CUDA(lb_launch_overlapped(latent_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, d, ldd, gain, freq, positions, slot_mapping,
-                                           (float*)cache, rank, rot, rot_dims, eps));
+                                           (float*)cache, rank, rot, rot_dims, eps, interleaved));
     else if (cache_dtype == LB_BF16)
         LB_CHECK_CUDA(lb_launch_overlapped(latent_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, d, ldd, gain, freq, positions,
-                                           slot_mapping, (__nv_bfloat16*)cache, rank, rot, rot_dims, eps));
+                                           slot_mapping, (__nv_bfloat16*)cache, rank, rot, rot_dims, eps, interleaved));
     else return lb_fail(LB_ERR_INVALID_ARGUMENT, "latent store: unknown dtype %d", cache_dtype);
     return LB_OK;
 }
@@ -427,6 +457,14 @@ extern "C" int lb_latent_few_supports(int dim, int rot, int rank, int vdim, int 
 extern "C" int lb_latent_prepare(const float* qd, int64_t ldq, const void* uk, const float* gain, const float* freq, const int32_t* positions,
                                  const int32_t* slot_mapping, void* cache, void* wide, int64_t ldw, int n_tokens, int n_head, int dim, int rot, int rot_dims,
                                  int rank, float eps, void* stream) {
+    return lb_latent_prepare_ext(qd, ldq, uk, gain, freq, positions, slot_mapping, cache, wide, ldw, n_tokens, n_head, dim, rot, rot_dims, rank, eps, nullptr,
+                                 stream);
+}
+
+extern "C" int lb_latent_prepare_ext(const float* qd, int64_t ldq, const void* uk, const float* gain, const float* freq, const int32_t* positions,
+                                     const int32_t* slot_mapping, void* cache, void* wide, int64_t ldw, int n_tokens, int n_head, int dim, int rot,
+                                     int rot_dims, int rank, float eps, const lb_latent_extras* extras, void* stream) {
+    const lb_latent_extras x = extras != nullptr ? *extras : lb_latent_extras{};
     LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_head < 65535 && dim >= 0 && rot >= 0 && rot_dims <= rot && rot_dims % 2 == 0 && rank > 0,
                  "latent queries: bad sizes heads=%d dim=%d rot=%d rotated=%d", n_head, dim, rot, rot_dims);
     if (n_tokens == 0) return LB_OK;
@@ -436,33 +474,44 @@ extern "C" int lb_latent_prepare(const float* qd, int64_t ldq, const void* uk, c
     if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     LB_CHECK_CUDA(lb_launch_overlapped(latent_prepare_kernel, grid, dim3(128), smem, static_cast<cudaStream_t>(stream), qd, ldq,
                                        (const __nv_bfloat16*)uk, gain, freq, positions, slot_mapping, (__nv_bfloat16*)cache, (__nv_bfloat16*)wide, ldw, n_head, dim,
-                                       rot, rot_dims, rank, eps, n_head * (dim + rot)));
+                                       rot, rot_dims, rank, eps, n_head * (dim + rot), x.latent, x.ldl, x.interleaved));
     return LB_OK;
 }
 
 extern "C" int lb_latent_finish(const float* attended, int64_t lda, const float* part_o, const float* part_ml, const void* uv, void* values, int64_t ldv,
                                 int n_tokens, int n_head, int rank, int vdim, int n_splits, void* stream) {
+    return lb_latent_finish_ext(attended, lda, part_o, part_ml, uv, values, ldv, n_tokens, n_head, rank, vdim, n_splits, nullptr, stream);
+}
+
+extern "C" int lb_latent_finish_ext(const float* attended, int64_t lda, const float* part_o, const float* part_ml, const void* uv, void* values,
+                                    int64_t ldv, int n_tokens, int n_head, int rank, int vdim, int n_splits, const lb_latent_extras* extras, void* stream) {
+    const lb_latent_extras x = extras != nullptr ? *extras : lb_latent_extras{};
     LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_head <= 65535 && rank > 0 && rank % 8 == 0 && vdim > 0 && n_splits >= 1 && n_splits <= 32,
                  "latent values: bad sizes heads=%d rank=%d vdim=%d parts=%d", n_head, rank, vdim, n_splits);
     if (n_tokens == 0) return LB_OK;
     LB_CHECK_CUDA(lb_launch_overlapped(latent_finish_kernel, dim3(n_tokens, n_head), dim3(128), (size_t)(rank + 32) * sizeof(float), static_cast<cudaStream_t>(stream),
                                        attended, lda, part_o, part_ml, (const __nv_bfloat16*)uv, (__nv_bfloat16*)values, ldv, n_tokens, n_head, rank, vdim,
-                                       n_splits));
+                                       n_splits, x.sink, x.gate, x.ldg));
     return LB_OK;
 }
 
 extern "C" int lb_rope_heads(int q_dtype, int wide_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, void* wide, int64_t ldw,
                              int n_tokens, int n_head, int dim, int rot, int rot_dims, int rank, void* stream) {
+    return lb_rope_heads_ext(q_dtype, wide_dtype, q, ldq, freq, positions, wide, ldw, n_tokens, n_head, dim, rot, rot_dims, rank, 0, stream);
+}
+
+extern "C" int lb_rope_heads_ext(int q_dtype, int wide_dtype, const void* q, int64_t ldq, const float* freq, const int32_t* positions, void* wide,
+                                 int64_t ldw, int n_tokens, int n_head, int dim, int rot, int rot_dims, int rank, int interleaved, void* stream) {
     LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && dim >= 0 && rot >= 0 && rot_dims <= rot && rot_dims % 2 == 0 && rank > 0,
                  "rotation of queries: bad sizes heads=%d dim=%d rot=%d rotated=%d", n_head, dim, rot, rot_dims);
     if (n_tokens == 0 || rot == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
     if (q_dtype == LB_F32 && wide_dtype == LB_F32)
         LB_CHECK_CUDA(lb_launch_overlapped(rope_heads_kernel<float, float>, dim3(n_tokens), dim3(128), 0, s, (const float*)q, ldq, freq, positions,
-                                           (float*)wide, ldw, n_head, dim, rot, rot_dims, rank));
+                                           (float*)wide, ldw, n_head, dim, rot, rot_dims, rank, interleaved));
     else if (q_dtype == LB_F32 && wide_dtype == LB_BF16)
         LB_CHECK_CUDA(lb_launch_overlapped(rope_heads_kernel<float, __nv_bfloat16>, dim3(n_tokens), dim3(128), 0, s, (const float*)q, ldq, freq, positions,
-                                           (__nv_bfloat16*)wide, ldw, n_head, dim, rot, rot_dims, rank));
+                                           (__nv_bfloat16*)wide, ldw, n_head, dim, rot, rot_dims, rank, interleaved));
     else return lb_fail(LB_ERR_UNSUPPORTED, "rotation of queries: element types %d -> %d are not built", q_dtype, wide_dtype);
     return LB_OK;
 }
@@ -485,15 +534,24 @@ extern "C" int lb_head_matmul(int a_dtype, int b_dtype, int c_dtype, const void*
 extern "C" int lb_latent_attention(int cache_dtype, const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq,
                                    const int32_t* positions, const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens,
                                    int n_head, int rank, int rot, int page_size, float scale, int window, void* stream) {
+    return lb_latent_attention_ext(cache_dtype, wide, ldw, cache, tok_seq, positions, block_table, table_stride, out, ldo, n_tokens, n_head, rank, rot,
+                                   page_size, scale, window, nullptr, stream);
+}
+
+extern "C" int lb_latent_attention_ext(int cache_dtype, const float* wide, int64_t ldw, const void* cache, const int32_t* tok_seq,
+                                       const int32_t* positions, const int32_t* block_table, int table_stride, float* out, int64_t ldo, int n_tokens,
+                                       int n_head, int rank, int rot, int page_size, float scale, int window, const lb_latent_extras* extras,
+                                       void* stream) {
+    const lb_latent_extras x = extras != nullptr ? *extras : lb_latent_extras{};
     LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && rank > 0 && rot >= 0 && page_size > 0 && window >= 0,
                  "latent attention: bad sizes heads=%d rank=%d rot=%d page=%d window=%d", n_head, rank, rot, page_size, window);
     if (n_tokens == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
     if (cache_dtype == LB_F32)
         return pick_latent_attention<float>(wide, ldw, cache, tok_seq, positions, block_table, table_stride, out, ldo, n_tokens, n_head, rank, rot,
-                                            page_size, scale, window, s);
+                                            page_size, scale, window, x.sink, x.gate, x.ldg, s);
     if (cache_dtype == LB_BF16)
         return pick_latent_attention<__nv_bfloat16>(wide, ldw, cache, tok_seq, positions, block_table, table_stride, out, ldo, n_tokens, n_head, rank,
-                                                    rot, page_size, scale, window, s);
+                                                    rot, page_size, scale, window, x.sink, x.gate, x.ldg, s);
     return lb_fail(LB_ERR_INVALID_ARGUMENT, "latent attention: unknown dtype %d", cache_dtype);
 }

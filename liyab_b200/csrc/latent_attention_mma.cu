@@ -48,13 +48,31 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
+// What a (token, head)'s sums are multiplied by at the end.  Without extras 1 / l.  A head's sink adds exp(sink) to the divisor (it has no
+// key and no value; `m`, the running maximum, is in the scores' base-2 scale); a gate multiplies the result by sigmoid(gate[t, head]).
+struct HeadExtras {
+    const float* sink;
+    const float* gate;
+    int64_t ldg;
+};
+__device__ __forceinline__ float finish_factor(const HeadExtras& x, int t, int head, float m, float l) {
+    float f = 1.0f;
+    if (x.sink != nullptr) {
+        const float sk = x.sink[head] * 1.4426950408889634f, top = fmaxf(m, sk);
+        f = exp2f(m - top);
+        l = l * f + exp2f(sk - top);
+    }
+    if (x.gate != nullptr) f *= 1.0f / (1.0f + expf(-x.gate[(size_t)t * x.ldg + head]));
+    return f / l;
+}
+
 // MT: 16-row tiles of a block; RT: 8-column tiles of the rank values per warp (rank = 32 * RT).
 template <int MT, int RT>
 __global__ void __launch_bounds__(128)
 latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf16* __restrict__ cache, const int32_t* __restrict__ q_start,
                             const int32_t* __restrict__ n_past, const int32_t* __restrict__ block_table, int table_stride,
                             float* __restrict__ out, int64_t ldo, float* __restrict__ part_o, float* __restrict__ part_ml, int n_tokens,
-                            int n_head, int rot, int page_size, float scale_log2, int window, int HB, int n_splits) {
+                            int n_head, int rot, int page_size, float scale_log2, int window, int HB, int n_splits, HeadExtras extras) {
     constexpr int M = 16 * MT, RANK = 32 * RT;
     const int D = RANK + rot, DS = D + 8, chunks = D / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -226,7 +244,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf
             if (tok >= n_here || head >= n_head) continue;
             const int t = first + tok;
             if (n_splits == 1) {
-                const float inv = 1.0f / l_run[mt][half];
+                const float inv = finish_factor(extras, t, head, m_run[mt][half], l_run[mt][half]);
                 float* dst = out + (size_t)t * ldo + (size_t)head * RANK + warp * RT * 8 + 2 * t4;
 #pragma unroll
                 for (int nt = 0; nt < RT; ++nt)
@@ -252,7 +270,7 @@ template <int N8, typename TO>
 __global__ void __launch_bounds__(128)
 latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const bf16* __restrict__ cache, const int32_t* __restrict__ q_start,
                              const int32_t* __restrict__ n_past, const int32_t* __restrict__ block_table, int table_stride, TO* __restrict__ out,
-                             int64_t ldo, int n_head, int rot, int page_size, float scale_log2, int window, int HB) {
+                             int64_t ldo, int n_head, int rot, int page_size, float scale_log2, int window, int HB, HeadExtras extras) {
     constexpr int M = 64, RANK = 8 * N8;
     const int D = RANK + rot, DS = D + 8, chunks = D / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -398,7 +416,7 @@ latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const b
     for (int half = 0; half < 2; ++half) {
         const int row = warp * 16 + g + 8 * half, tok = row / HB, head = hg * HB + row % HB;
         if (tok >= n_here || head >= n_head) continue;
-        const float inv = 1.0f / l_run[half];
+        const float inv = finish_factor(extras, first + tok, head, m_run[half], l_run[half]);
         TO* dst = out + (size_t)(first + tok) * ldo + (size_t)head * RANK + 2 * t4;
 #pragma unroll
         for (int nt = 0; nt < N8; ++nt) {
@@ -410,20 +428,21 @@ latent_attention_rows_kernel(const bf16* __restrict__ wide, int64_t ldw, const b
 
 template <int N8, typename TO>
 int launch_rows(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table, int table_stride,
-                TO* out, int64_t ldo, int n_seq, int max_q_len, int n_head, int rot, int page_size, float scale, int window, cudaStream_t s) {
+                TO* out, int64_t ldo, int n_seq, int max_q_len, int n_head, int rot, int page_size, float scale, int window, HeadExtras extras,
+                cudaStream_t s) {
     // Up to sixteen heads of a token side by side (more heads: groups of equal size), then the next tokens.
     const int groups = (n_head + 15) / 16, HB = (n_head + groups - 1) / groups, TOK = 64 / HB, DS = 8 * N8 + rot + 8;
     const size_t smem = (size_t)(64 + 2 * kKeys) * DS * sizeof(bf16);
     if (smem > 48 * 1024) LB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_rows_kernel<N8, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid((max_q_len + TOK - 1) / TOK, n_seq, (n_head + HB - 1) / HB);
     LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_rows_kernel<N8, TO>, grid, dim3(128), smem, s, (const bf16*)wide, ldw, (const bf16*)cache, q_start, n_past,
-                                       block_table, table_stride, out, ldo, n_head, rot, page_size, scale * 1.4426950408889634f, window, HB));
+                                       block_table, table_stride, out, ldo, n_head, rot, page_size, scale * 1.4426950408889634f, window, HB, extras));
     return LB_OK;
 }
 
 // out[t, h, :] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the parts, in their order.
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out, int64_t ldo,
-                                    int n_tokens, int n_head, int rank, int n_splits) {
+                                    int n_tokens, int n_head, int rank, int n_splits, HeadExtras extras) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -435,7 +454,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
         const float ms = part_ml[at * 2];
         if (ms != -CUDART_INF_F) l += exp2f(ms - m) * part_ml[at * 2 + 1];
     }
-    const float inv = 1.0f / l;
+    const float inv = finish_factor(extras, t, h, m, l);
     for (int d = threadIdx.x; d < rank; d += blockDim.x) {
         float acc = 0.0f;
         for (int s = 0; s < n_splits; ++s) {
@@ -530,7 +549,7 @@ size_t mma_smem_bytes(int m, int rank, int rot) {
 template <int MT, int RT>
 int launch_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
                int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, int n_head, int rot,
-               int page_size, float scale, int window, int n_splits, bool merge_parts, cudaStream_t s) {
+               int page_size, float scale, int window, int n_splits, bool merge_parts, HeadExtras extras, cudaStream_t s) {
     constexpr int M = 16 * MT;
     const int groups = (n_head + 15) / 16, HB = (n_head + groups - 1) / groups, TOK = M / HB;
     const size_t smem = mma_smem_bytes(M, 32 * RT, rot);
@@ -538,10 +557,10 @@ int launch_mma(const void* wide, int64_t ldw, const void* cache, const int32_t* 
     const dim3 grid((max_q_len + TOK - 1) / TOK, n_seq, ((n_head + HB - 1) / HB) * n_splits);
     LB_CHECK_CUDA(lb_launch_overlapped(latent_attention_mma_kernel<MT, RT>, grid, dim3(128), smem, s, (const bf16*)wide, ldw, (const bf16*)cache, q_start,
                                        n_past, block_table, table_stride, out, ldo, part_o, part_ml, n_tokens, n_head, rot, page_size,
-                                       scale * 1.4426950408889634f, window, HB, n_splits));
+                                       scale * 1.4426950408889634f, window, HB, n_splits, extras));
     if (n_splits > 1 && merge_parts)            // else the caller merges the parts itself (lb_latent_finish)
         LB_CHECK_CUDA(lb_launch_overlapped(latent_merge_kernel, dim3(n_tokens, n_head), dim3(128), 0, s, (const float*)part_o, (const float*)part_ml, out, ldo,
-                                           n_tokens, n_head, 32 * RT, n_splits));
+                                           n_tokens, n_head, 32 * RT, n_splits, extras));
     return LB_OK;
 }
 
@@ -600,13 +619,22 @@ extern "C" int lb_latent_attention_rows_supports(int n_head, int rank, int rot, 
 extern "C" int lb_latent_attention_rows16(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
                                           const int32_t* block_table, int table_stride, void* out, int64_t ldo, int n_tokens, int n_seq, int max_q_len,
                                           int n_head, int rank, int rot, int page_size, float scale, int window, void* stream) {
+    return lb_latent_attention_rows16_ext(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, n_tokens, n_seq, max_q_len, n_head, rank, rot,
+                                          page_size, scale, window, nullptr, stream);
+}
+
+extern "C" int lb_latent_attention_rows16_ext(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                              const int32_t* block_table, int table_stride, void* out, int64_t ldo, int n_tokens, int n_seq,
+                                              int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window,
+                                              const lb_latent_extras* x, void* stream) {
+    const HeadExtras extras = x != nullptr ? HeadExtras{x->sink, x->gate, x->ldg} : HeadExtras{nullptr, nullptr, 0};
     if (!lb_latent_attention_rows_supports(n_head, rank, rot, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "latent attention, 64 rows a block: rank %d, rot %d are not built", rank, rot);
     if (n_tokens == 0 || n_seq == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
 #define LB_ROWS16(N8) \
     if (rank == 8 * N8) return launch_rows<N8, bf16>(wide, ldw, cache, q_start, n_past, block_table, table_stride, (bf16*)out, ldo, n_seq, max_q_len, n_head, rot, \
-                                                     page_size, scale, window, s)
+                                                     page_size, scale, window, extras, s)
     LB_ROWS16(4); LB_ROWS16(8); LB_ROWS16(12); LB_ROWS16(16); LB_ROWS16(24); LB_ROWS16(32);
 #undef LB_ROWS16
     return lb_fail(LB_ERR_UNSUPPORTED, "latent attention, 64 rows a block: rank %d is not built", rank);
@@ -616,6 +644,17 @@ extern "C" int lb_latent_attention_mma(const void* wide, int64_t ldw, const void
                                        const int32_t* block_table, int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml,
                                        int n_tokens, int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window,
                                        int n_splits, int merge_parts, void* stream) {
+    return lb_latent_attention_mma_ext(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, part_o, part_ml, n_tokens, n_seq, max_q_len,
+                                       n_head, rank, rot, page_size, scale, window, n_splits, merge_parts, nullptr, stream);
+}
+
+// With extras: a part of split keys is left as it is (its maximum and sum travel with it); the sink and the gate act where the parts
+// meet (the merge here, or lb_latent_finish_ext), or at once where the keys are not split.
+extern "C" int lb_latent_attention_mma_ext(const void* wide, int64_t ldw, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                           const int32_t* block_table, int table_stride, float* out, int64_t ldo, float* part_o, float* part_ml,
+                                           int n_tokens, int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window,
+                                           int n_splits, int merge_parts, const lb_latent_extras* x, void* stream) {
+    const HeadExtras extras = x != nullptr ? HeadExtras{x->sink, x->gate, x->ldg} : HeadExtras{nullptr, nullptr, 0};
     if (!lb_latent_attention_mma_supports(n_head, rank, rot, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "latent attention on tensor cores: rank %d, rot %d are not built", rank, rot);
     LB_CHECK_ARG(n_tokens >= 0 && n_seq >= 0 && max_q_len >= 0 && n_splits >= 1 && out != nullptr && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
@@ -626,14 +665,14 @@ extern "C" int lb_latent_attention_mma(const void* wide, int64_t ldw, const void
     if (max_q_len > 1 && n_splits == 1 && rank <= 256 && (size_t)(64 + 2 * kKeys) * (rank + rot + 8) * sizeof(bf16) <= 200 * 1024) {
 #define LB_ROWS(N8) \
     if (rank == 8 * N8) return launch_rows<N8, float>(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, n_seq, max_q_len, n_head, rot, page_size, \
-                                               scale, window, s)
+                                               scale, window, extras, s)
         LB_ROWS(4); LB_ROWS(8); LB_ROWS(12); LB_ROWS(16); LB_ROWS(24); LB_ROWS(32);
 #undef LB_ROWS
     }
     // Else two 16-row tiles a block where a request brings several tokens; one otherwise.
     const bool two = max_q_len > 1;
 #define LB_MMA(MT, RT) return launch_mma<MT, RT>(wide, ldw, cache, q_start, n_past, block_table, table_stride, out, ldo, part_o, part_ml, n_tokens, n_seq, \
-                                                 max_q_len, n_head, rot, page_size, scale, window, n_splits, merge_parts != 0, s)
+                                                 max_q_len, n_head, rot, page_size, scale, window, n_splits, merge_parts != 0, extras, s)
 #define LB_MMA_RANK(RT)            \
     if (rank == 32 * RT) {         \
         if (two) LB_MMA(2, RT);    \

@@ -1,0 +1,240 @@
+// Row-wise pieces around attention whose queries and keys are normed over the whole projection and rotated, whose values
+// blend with an earlier layer's, and around mixers whose heads are normed together: queries, keys and values on their way
+// to the attention kernels and the cache; the norm over all heads with a gate; an activation over some columns of a
+// projection; and the experts of a row looked up by its token id.  Statistics, angles, gates and activations are 32-bit
+// whatever the element type of the rows.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float rr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------- queries, keys and values: norm, rotation, blend, store
+// A block per token.  From the float row [.. q (H x D) .. k (G x D) .. v (G x E) ..]:
+//   norm_mode 0: queries and keys as they are; 1: every head over its own root mean square, gains [D] shared by the heads;
+//   2: all of q (and all of k) over one root mean square, gains [H x D] and [G x D];
+//   then the first rot_dims values of every query and key head are rotated, value i with value i + rot_dims / 2, by the
+//   angle position * freq[i];
+//   values: with v_first_in, v = (1 - lambda) v + lambda v_first_in[t]; with v_first_out, the row's own values are left there.
+// Queries go to q_out [H x P] (P >= D, E; the rest zeros), keys and values into the cache [page][K|V][G][slot][P].
+template <typename T>
+__global__ void qkv_rotary_store_kernel(const float* __restrict__ proj, int64_t ld, int q_off, int k_off, int v_off, const float* __restrict__ qw,
+                                        const float* __restrict__ kw, T* __restrict__ q_out, int64_t ldq, T* __restrict__ cache,
+                                        const int32_t* __restrict__ slot_mapping, int H, int G, int D, int E, int P, int page_size, int norm_mode, float eps,
+                                        const int32_t* __restrict__ positions, const float* __restrict__ freq, int rot_dims,
+                                        const float* __restrict__ v_first_in, float* __restrict__ v_first_out, int64_t ldv, const float* __restrict__ lambda) {
+    __shared__ float scratch[33];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const float* row = proj + (size_t)t * ld;
+    const int pos = positions != nullptr ? positions[t] : 0;
+    const int half = rot_dims / 2;
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (norm_mode == 2) {
+        float sq = 0.0f, sk = 0.0f;
+        for (int i = threadIdx.x; i < H * D; i += blockDim.x) sq = fmaf(row[q_off + i], row[q_off + i], sq);
+        for (int i = threadIdx.x; i < G * D; i += blockDim.x) sk = fmaf(row[k_off + i], row[k_off + i], sk);
+        inv_q = 1.0f / sqrtf(lb_block_sum(sq, scratch) / (float)(H * D) + eps);
+        inv_k = 1.0f / sqrtf(lb_block_sum(sk, scratch) / (float)(G * D) + eps);
+    }
+    const int slot = cache != nullptr ? slot_mapping[t] : -1;
+    const size_t plane = (size_t)G * page_size * P;
+    const float lam = v_first_in != nullptr ? lambda[0] : 0.0f;
+    for (int job = warp; job < H + 2 * G; job += n_warps) {
+        if (job >= H + G) {                     // a value head
+            const int g = job - H - G;
+            const float* src = row + v_off + (size_t)g * E;
+            T* dst = nullptr;
+            if (slot >= 0) {
+                const int page = slot / page_size, off = slot - page * page_size;
+                dst = cache + (size_t)page * 2 * plane + plane + ((size_t)g * page_size + off) * P;
+            }
+            for (int d = lane; d < P; d += 32) {
+                float v = 0.0f;
+                if (d < E) {
+                    v = src[d];
+                    if (v_first_out != nullptr) v_first_out[(size_t)t * ldv + (size_t)g * E + d] = v;
+                    if (v_first_in != nullptr) v = (1.0f - lam) * v + lam * v_first_in[(size_t)t * ldv + (size_t)g * E + d];
+                }
+                if (dst != nullptr) dst[d] = lb_from_float<T>(v);
+            }
+            continue;
+        }
+        const bool is_q = job < H;
+        const int head = is_q ? job : job - H;
+        if (!is_q && slot < 0) continue;
+        const float* src = row + (is_q ? q_off : k_off) + (size_t)head * D;
+        const float* gain = is_q ? qw : kw;
+        if (gain != nullptr && norm_mode == 2) gain += (size_t)head * D;
+        T* dst;
+        if (is_q) {
+            dst = q_out + (size_t)t * ldq + (size_t)head * P;
+        } else {
+            const int page = slot / page_size, off = slot - page * page_size;
+            dst = cache + (size_t)page * 2 * plane + ((size_t)head * page_size + off) * P;
+        }
+        float inv = is_q ? inv_q : inv_k;
+        if (norm_mode == 1) {
+            float ss = 0.0f;
+            for (int d = lane; d < D; d += 32) ss = fmaf(src[d], src[d], ss);
+            inv = 1.0f / sqrtf(lb_warp_sum(ss) / (float)D + eps);
+        }
+        auto normed = [&](int d) {
+            float v = src[d] * inv;
+            if (norm_mode != 0 && gain != nullptr) v *= gain[d];
+            return v;
+        };
+        for (int d = lane; d < P; d += 32) {
+            float v = 0.0f;
+            if (d < D) {
+                if (d < rot_dims) {
+                    const int i = d < half ? d : d - half;
+                    float sn, cs;
+                    sincosf((float)pos * freq[i], &sn, &cs);
+                    const float lo = normed(i), hi = normed(i + half);
+                    v = d < half ? lo * cs - hi * sn : hi * cs + lo * sn;
+                } else {
+                    v = normed(d);
+                }
+            }
+            dst[d] = lb_from_float<T>(v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- out = rms(o over the whole row) * gain * gate(g)
+// A block per row; rows of up to four values a thread stay in registers between the sum of squares and the write.
+template <typename TO>
+__global__ void row_norm_gate_kernel(const float* __restrict__ o, int64_t ldo, const float* __restrict__ g, int64_t ldg, const float* __restrict__ gain,
+                                     TO* __restrict__ out, int64_t ld_out, int width, int act, float eps) {
+    __shared__ float scratch[33];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int r = blockIdx.x;
+    const float* src = o + (size_t)r * ldo;
+    constexpr int kKeep = 4;
+    const bool kept = width <= kKeep * (int)blockDim.x;
+    float held[kKeep];
+    float ss = 0.0f;
+    if (kept) {
+#pragma unroll
+        for (int e = 0; e < kKeep; ++e) {
+            const int c = threadIdx.x + e * blockDim.x;
+            held[e] = c < width ? src[c] : 0.0f;
+            ss = fmaf(held[e], held[e], ss);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(src[c], src[c], ss);
+    }
+    const float inv = 1.0f / sqrtf(lb_block_sum(ss, scratch) / (float)width + eps);
+    auto finish = [&](int c, float v) {
+        v *= inv;
+        if (gain != nullptr) v *= gain[c];
+        if (g != nullptr) {
+            const float z = g[(size_t)r * ldg + c];
+            v *= act == LB_GATE_SILU ? z * rr_sigmoid(z) : rr_sigmoid(z);
+        }
+        out[(size_t)r * ld_out + c] = lb_from_float<TO>(v);
+    };
+    if (kept) {
+#pragma unroll
+        for (int e = 0; e < kKeep; ++e) {
+            const int c = threadIdx.x + e * blockDim.x;
+            if (c < width) finish(c, held[e]);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) finish(c, src[c]);
+    }
+}
+
+// ---------------------------------------------------------------- x[r, c] = act(x[r, c]) for c < cols, in place
+__global__ void activate_columns_kernel(float* __restrict__ x, int64_t ld, int n_rows, int cols, int act) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const long total = (long)n_rows * cols;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / cols;
+        const int c = (int)(i - r * cols);
+        float* at = x + (size_t)r * ld + c;
+        const float z = *at;
+        *at = act == LB_GATE_SILU ? z * rr_sigmoid(z) : act == LB_GATE_GELU_TANH ? lb_gelu_tanh(z) : act == LB_GATE_RELU ? fmaxf(z, 0.0f) : rr_sigmoid(z);
+    }
+}
+
+// ---------------------------------------------------------------- a row's experts from a table by token id, equal weights
+__global__ void router_table_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ table, int32_t* __restrict__ ids,
+                                    float* __restrict__ weights, int n_rows, int top, int n_experts, int vocab) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows * top) return;
+    const int r = i / top, j = i - r * top;
+    const int tok = min(max(tokens[r], 0), vocab - 1);
+    // An entry outside the experts would send the products out of their matrices: it is kept inside (a file with such a table is refused at load).
+    ids[i] = min(max(table[(size_t)tok * top + j], 0), n_experts - 1);
+    weights[i] = 1.0f / (float)top;
+}
+
+int rr_grid(long total, int threads) { return (int)min((total + threads - 1) / threads, (long)148 * 16); }
+
+}  // namespace
+
+extern "C" int lb_qkv_rotary_store(int dtype, const float* proj, int64_t ld, int q_off, int k_off, int v_off, const float* q_weight, const float* k_weight,
+                                   void* q_out, int64_t ldq, void* cache, const int32_t* slot_mapping, int n_tokens, int n_head, int n_kv_head, int dim,
+                                   int vdim, int padded, int page_size, int norm_mode, float eps, const int32_t* positions, const float* freq, int rot_dims,
+                                   const float* v_first_in, float* v_first_out, int64_t ldv, const float* lambda, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_kv_head > 0 && dim > 0 && vdim > 0 && padded >= dim && padded >= vdim && page_size > 0,
+                 "qkv_rotary_store: bad sizes heads=%d/%d dim=%d vdim=%d padded=%d", n_head, n_kv_head, dim, vdim, padded);
+    LB_CHECK_ARG(norm_mode >= 0 && norm_mode <= 2, "qkv_rotary_store: norm mode %d (0 none, 1 a head, 2 the whole projection)", norm_mode);
+    LB_CHECK_ARG(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || (freq != nullptr && positions != nullptr)),
+                 "qkv_rotary_store: %d of %d values cannot be rotated in pairs, or no frequencies and positions were given", rot_dims, dim);
+    LB_CHECK_ARG(v_first_in == nullptr || lambda != nullptr, "qkv_rotary_store: a blend of values needs its weight");
+    if (n_tokens == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const int jobs = n_head + 2 * n_kv_head, threads = 32 * min(8, jobs);
+    if (dtype == LB_F32)
+        LB_CHECK_CUDA(lb_launch_overlapped(qkv_rotary_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, proj, ld, q_off, k_off, v_off, q_weight, k_weight,
+                                           (float*)q_out, ldq, (float*)cache, slot_mapping, n_head, n_kv_head, dim, vdim, padded, page_size, norm_mode, eps,
+                                           positions, freq, rot_dims, v_first_in, v_first_out, ldv, lambda));
+    else if (dtype == LB_BF16)
+        LB_CHECK_CUDA(lb_launch_overlapped(qkv_rotary_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, proj, ld, q_off, k_off, v_off, q_weight,
+                                           k_weight, (__nv_bfloat16*)q_out, ldq, (__nv_bfloat16*)cache, slot_mapping, n_head, n_kv_head, dim, vdim, padded,
+                                           page_size, norm_mode, eps, positions, freq, rot_dims, v_first_in, v_first_out, ldv, lambda));
+    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "qkv_rotary_store: unknown dtype %d", dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_row_norm_gate(int out_dtype, const float* o, int64_t ldo, const float* g, int64_t ldg, const float* gain, void* out, int64_t ld_out,
+                                int n_rows, int width, int act, float eps, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && width > 0 && (act == LB_GATE_SIGMOID || act == LB_GATE_SILU), "row_norm_gate: bad sizes width=%d act=%d", width, act);
+    if (n_rows == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const int threads = width > 512 ? 256 : 128;
+    if (out_dtype == LB_F32)
+        LB_CHECK_CUDA(lb_launch_overlapped(row_norm_gate_kernel<float>, dim3(n_rows), dim3(threads), 0, s, o, ldo, g, ldg, gain, (float*)out, ld_out, width, act, eps));
+    else if (out_dtype == LB_BF16)
+        LB_CHECK_CUDA(lb_launch_overlapped(row_norm_gate_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s, o, ldo, g, ldg, gain, (__nv_bfloat16*)out, ld_out,
+                                           width, act, eps));
+    else return lb_fail(LB_ERR_INVALID_ARGUMENT, "row_norm_gate: unknown dtype %d", out_dtype);
+    return LB_OK;
+}
+
+extern "C" int lb_activate_columns(float* x, int64_t ld, int n_rows, int cols, int act, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && cols > 0 && act >= LB_GATE_SIGMOID && act <= LB_GATE_RELU, "activate_columns: bad sizes cols=%d act=%d", cols, act);
+    if (n_rows == 0) return LB_OK;
+    LB_CHECK_CUDA(lb_launch_overlapped(activate_columns_kernel, dim3(rr_grid((long)n_rows * cols, 256)), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ld,
+                                       n_rows, cols, act));
+    return LB_OK;
+}
+
+extern "C" int lb_router_table(const int32_t* tokens, const int32_t* table, int32_t* ids, float* weights, int n_rows, int top, int n_experts, int vocab,
+                               void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && top > 0 && n_experts > 0 && vocab > 0, "router_table: bad sizes top=%d experts=%d vocab=%d", top, n_experts, vocab);
+    if (n_rows == 0) return LB_OK;
+    const int total = n_rows * top;
+    LB_CHECK_CUDA(lb_launch_overlapped(router_table_kernel, dim3((total + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), tokens, table, ids, weights,
+                                       n_rows, top, n_experts, vocab));
+    return LB_OK;
+}

@@ -57,6 +57,7 @@ void register_gpt2();      // gpt2.cpp
 void register_puzutar();   // puzutar.cpp
 void register_vosurax();   // vosurax.cpp
 void register_viresun();   // viresun.cpp
+void register_revudra();   // revudra.cpp
 
 void register_architecture(Architecture arch) { table()[arch.name] = std::move(arch); }
 
@@ -67,6 +68,7 @@ void register_builtin_architectures() {
         register_puzutar();
         register_vosurax();
         register_viresun();
+        register_revudra();
         register_architecture({"liyab_spec", {}, [](const Json& raw) { return std::make_unique<SpecConfig>(raw); }});
     });
     // Plug-ins named by the environment (paths separated by ':') are loaded once, so that the programs can run

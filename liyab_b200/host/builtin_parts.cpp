@@ -62,6 +62,9 @@ void register_builtin_parts() {
         arrangements().add("parallel", {[](const LayerSpec& l, const LayerParts& parts, const Runtime&) {
                                return std::make_shared<ParallelBlock>(l, parts);
                            }});
+        arrangements().add("sublayer_norm", {[](const LayerSpec& l, const LayerParts& parts, const Runtime&) {
+                               return std::make_shared<SublayerNormBlock>(l, parts);
+                           }});
         arrangements().add("pre_norm", {[](const LayerSpec& l, const LayerParts& parts, const Runtime&) {
                                return std::make_shared<PreNormBlock>(l, parts);
                            }});

@@ -239,7 +239,7 @@ public:
 };
 
 // ---- the dense, ungated feed-forward: down(act(up(x))) ----------------------------------------------
-// Activations, all in the first product's epilogue: gelu_tanh, gelu_erf, none and xielu (z > 0: softplus(p) z^2 + z/2; else
+// Activations, all in the first product's epilogue: gelu_tanh, gelu_erf, relu2 (the square of relu), none and xielu (z > 0: softplus(p) z^2 + z/2; else
 // (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2, with the learned pair `act` = (p, q), which the product finds behind its bias).
 // Reference: dense_ffn, ungated branch (src/core/transformer.cpp:4903-4913) with the activations of :125-142.
 // Bias and activation ride in the first product's epilogue, bias and the residual sum in the second's.
@@ -274,6 +274,13 @@ public:
             up.forward(ctx, h, mid, T, activation);
         }
         down.forward(ctx, mid, x, T, kernels::kNone, &x);
+    }
+    void forward_into(StepContext& ctx, const Rows& h, const Rows& y) override {
+        if (xielu != nullptr) return FeedForward::forward_into(ctx, h, y);
+        const int T = ctx.n_tokens;
+        const Rows mid = ctx.workspace->get("ff.inner", T, inner, ctx.runtime.dtype);
+        up.forward(ctx, h, mid, T, activation);
+        down.forward(ctx, mid, y, T, kernels::kNone, nullptr);
     }
     // As the attention's: the up projection of a few tokens normalises the rows inside its kernel.
     bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x) override {
@@ -360,6 +367,72 @@ public:
     FeedForward* feed_forward = nullptr;
 
 private:
+    LayerParts keep_;
+};
+
+// `sublayer_norm`: the sublayers read the stream as it is, and what they put out passes a norm before it joins the stream:
+// x += m norm_a(mixer(x)); x += m norm_b(feed_forward(x)), with m the option `residual_scale` (default 1).  The stream stays
+// float32; in bfloat16 the sublayers read it rounded once.  Slots: mixer, mixer_norm (norm), and, unless the block has no
+// feed-forward, feed_forward and ff_norm (norm).  The norms are RMS norms over the whole row (a norm that offers that recipe):
+// norm, gain, scale and the sum into the stream are one pass over the sublayer's output.
+
+class SublayerNormBlock final : public Arrangement {
+public:
+    SublayerNormBlock(const LayerSpec& spec, const LayerParts& parts)
+        : mixer(parts.get<Mixer>("mixer")), mixer_norm(parts.get<Norm>("mixer_norm")), scale(static_cast<float>(spec.options.get_number("residual_scale", 1.0))),
+          keep_(parts) {
+        const bool with_ff = spec.find("feed_forward") != nullptr;
+        if (with_ff) {
+            feed_forward = &parts.get<FeedForward>("feed_forward");
+            ff_norm = &parts.get<Norm>("ff_norm");
+        }
+        if (spec.slots.size() != (with_ff ? 4u : 2u))
+            throw invalid_model("arrangement 'sublayer_norm' takes the slots mixer and mixer_norm, and feed_forward with ff_norm, only");
+        check(mixer_norm);
+        if (ff_norm != nullptr) check(*ff_norm);
+    }
+    bool capturable() const override {
+        return mixer_norm.capturable() && mixer.capturable() && (feed_forward == nullptr || (ff_norm->capturable() && feed_forward->capturable()));
+    }
+    std::vector<Mixer*> mixers() const override { return {&mixer}; }
+    void forward(StepContext& ctx, const Rows& x, CacheUnit unit) override {
+        const int T = ctx.n_tokens;
+        const Rows y = ctx.workspace->get("block.sublayer", T, x.cols, DType::F32);
+        ctx.phase(Phase::Mixer);
+        mixer.forward_into(ctx, input(ctx, x), y, unit);
+        ctx.tap("mixer.out", y);
+        join(ctx, mixer_norm, y, x);
+        ctx.tap("mixer", x);
+        if (feed_forward == nullptr) return;
+        ctx.phase(Phase::FeedForward);
+        feed_forward->forward_into(ctx, input(ctx, x), y);
+        ctx.tap("feed_forward.out", y);
+        join(ctx, *ff_norm, y, x);
+        ctx.tap("feed_forward", x);
+    }
+    Mixer& mixer;
+    Norm& mixer_norm;
+    FeedForward* feed_forward = nullptr;
+    Norm* ff_norm = nullptr;
+    float scale;
+
+private:
+    static void check(const Norm& n) {
+        const std::optional<NormRecipe> r = n.recipe();
+        if (!r || !r->rms || r->offset != nullptr || r->gain_offset != 0.0f)
+            throw unsupported("arrangement 'sublayer_norm' takes RMS norms over the whole row (gain only) on its sublayers' outputs");
+    }
+    // What a sublayer reads: the stream itself in float32, its rows rounded to the compute type otherwise.
+    Rows input(StepContext& ctx, const Rows& x) const {
+        if (ctx.runtime.dtype == DType::F32) return x;
+        const Rows h = ctx.workspace->get("block.input", ctx.n_tokens, x.cols, ctx.runtime.dtype);
+        kernels::rows_to_bf16(ctx.stream(), x, h, ctx.n_tokens);
+        return h;
+    }
+    void join(StepContext& ctx, const Norm& n, const Rows& y, const Rows& x) const {
+        const NormRecipe r = *n.recipe();
+        kernels::rms_sum_add(ctx.stream(), x, {y}, {r.gain}, ctx.n_tokens, scale, r.eps);
+    }
     LayerParts keep_;
 };
 

@@ -68,6 +68,12 @@ inline std::vector<float> rotation_frequencies(int dims, double base) {
 // `distance`: r1 for all heads, then r2) and the score of the key d positions back loses r1 ln(1 + r2 d).  With `qk_gain` false
 // the norm of queries and keys has no gain.  dim and vdim may differ: the cache and the attention kernels work on heads of
 // `padded` values, the rest zeros, so the existing kernels serve.
+// Further options.  `qk_norm_over` "projection": the norm runs over all of q (and all of k) at once instead of head by head, with gains of
+// n_head x dim and n_kv_head x dim values.  `rot_dims` r > 0: after the norm the first r values of every query and key head are rotated, value i
+// with value i + r/2, by the angle position * rot_base^(-2i/r).  `sink`: a learned number a head (the parameter `sink`) whose exponential
+// joins the divisor of the head's softmax; it has no key and no value and is not scaled.  `value_blend`: "source" leaves the step's values
+// (as projected) where later layers of the model find them; "blend" replaces its own by (1 - b) v + b v_source with the learned number `blend`
+// before they are cached.  The source is the model's first layer that says so; all such layers have n_kv_head x vdim values alike.
 
 class GatedAttention final : public Mixer {
 public:
@@ -101,6 +107,19 @@ public:
             k_gain = f32_or_null(&p.at("k_norm.weight"));
         }
         if (s.options.get_bool("distance_bias", false)) shape.distance = f32_or_null(&p.at("distance"));
+        const std::string over = s.options.get_string("qk_norm_over", "head");
+        if (over != "head" && over != "projection") throw unsupported("gated_attention: qk_norm_over '{}' is not supported; supported: head, projection", over);
+        norm_projection = qk_norm && over == "projection";
+        rot_dims = static_cast<int>(s.options.get_int("rot_dims", 0));
+        if (rot_dims < 0 || rot_dims > D || rot_dims % 2 != 0) throw invalid_model("gated_attention: {} of {} values cannot be rotated in pairs", rot_dims, D);
+        freq.host = rotation_frequencies(rot_dims, s.options.get_number("rot_base", 10000.0));
+        if (s.options.get_bool("sink", false)) shape.sink = f32_or_null(&p.at("sink"));
+        const std::string vb = s.options.get_string("value_blend", "none");
+        if (vb != "none" && vb != "source" && vb != "blend") throw unsupported("gated_attention: value_blend '{}' is not supported; supported: none, source, blend", vb);
+        blend_source = vb == "source";
+        if (vb == "blend") blend = f32_or_null(&p.at("blend"));
+        rotary_store = norm_projection || rot_dims > 0 || vb != "none";
+        if (rotary_store && temp_every > 0) throw unsupported("gated_attention: a temperature on the queries goes with neither rotation, norm over the projection nor blended values");
     }
     static std::vector<ParamDecl> parameters(const PartSpec& s) {
         const int64_t hidden = need_int(s, "hidden"), H = need_int(s, "n_head"), G = s.options.get_int("n_kv_head", H), D = need_int(s, "dim");
@@ -110,9 +129,12 @@ public:
         Linear::declare(out, "proj.", H * D + G * D + G * E + (gated ? H * E : 0), hidden, false);
         if (s.options.get_bool("bias", false)) out.push_back({"qkv_bias", {H * D + G * D + G * E}, ParamKind::Vector});
         if (s.options.get_bool("qk_norm", false) && s.options.get_bool("qk_gain", true)) {
-            out.push_back({"q_norm.weight", {D}, ParamKind::Vector});
-            out.push_back({"k_norm.weight", {D}, ParamKind::Vector});
+            const bool whole = s.options.get_string("qk_norm_over", "head") == "projection";
+            out.push_back({"q_norm.weight", {whole ? H * D : D}, ParamKind::Vector});
+            out.push_back({"k_norm.weight", {whole ? G * D : D}, ParamKind::Vector});
         }
+        if (s.options.get_bool("sink", false)) out.push_back({"sink", {H}, ParamKind::Vector});
+        if (s.options.get_string("value_blend", "none") == "blend") out.push_back({"blend", {1}, ParamKind::Vector});
         if (s.options.get_bool("distance_bias", false)) out.push_back({"distance", {2 * H}, ParamKind::Vector});
         Linear::declare(out, "out.", hidden, H * E, false);
         return out;
@@ -146,7 +168,9 @@ public:
     kernels::AttentionShape shape;
     int64_t hidden = 0;
     int H = 0, G = 0, D = 0, E = 0, gate = -1;
-    bool qk_norm = false;
+    bool qk_norm = false, norm_projection = false, blend_source = false, rotary_store = false;
+    int rot_dims = 0;
+    const float* blend = nullptr;
     float eps = 1e-6f, temp_coef = 0.0f;
     int temp_every = 0;
     Linear proj, out;
@@ -171,8 +195,17 @@ private:
         a.page_size = view->group->page_size;
         const Rows q = ws.get("gated_attention.q", T, static_cast<int64_t>(H) * P, dt);
         const kernels::QkvColumns cols{0, H * D, H * D + G * D, H, G, D, E, P, a.page_size};
-        kernels::qk_norm_store(s, pr, cols, q_gain, k_gain, q, unit.write ? cache : nullptr, view->slot_mapping, T, qk_norm, eps, ctx.positions, temp_coef,
-                               temp_every);
+        if (rotary_store) {
+            // The values that layers blend with travel from the source layer to the others in a buffer of the step.
+            Rows shared;
+            if (blend_source || blend != nullptr) shared = ws.get("gated_attention.value_source", T, static_cast<int64_t>(G) * E, DType::F32);
+            kernels::qkv_rotary_store(s, pr, cols, q_gain, k_gain, q, unit.write ? cache : nullptr, view->slot_mapping, T, !qk_norm ? 0 : norm_projection ? 2 : 1, eps,
+                                      ctx.positions, rot_dims > 0 ? freq.get(s) : nullptr, rot_dims, blend != nullptr ? &shared : nullptr,
+                                      blend_source ? &shared : nullptr, blend);
+        } else {
+            kernels::qk_norm_store(s, pr, cols, q_gain, k_gain, q, unit.write ? cache : nullptr, view->slot_mapping, T, qk_norm, eps, ctx.positions, temp_coef,
+                                   temp_every);
+        }
         ctx.tap("attention.q", q);
         const Rows att = ws.get("gated_attention.att", T, static_cast<int64_t>(H) * P, dt);
         const int reach = shape.chunk > 0 ? shape.chunk : shape.window;
@@ -188,6 +221,7 @@ private:
         kernels::linear(ctx.runtime, &ws, heads, out.weight, nullptr, y, T, kernels::kNone, residual);
     }
     PartialBias bias;
+    DeviceFloats freq;
 };
 
 // ---- a matrix memory per head ----------------------------------------------------------------------------------
@@ -200,6 +234,8 @@ private:
 // k_scale, after the rotation).  Every head's o is divided by its root mean square (`head_norm`), times a gain over all heads'
 // values where the part has one (`norm_gain`), times gate(g), then the output projection.
 // One projection makes [q | k | v | g | zi | zf] in 32-bit.
+// `qkv_activation` (silu, sigmoid, gelu_tanh, relu; default none) acts on q, k and v as they leave the projection.  `norm_over` "all": instead of
+// every head over its own root mean square, all heads' values together over one (with the gain `norm.weight` where `norm_gain` is set).
 
 class MatrixMemory final : public Mixer {
 public:
@@ -226,6 +262,14 @@ public:
         m.q_scale = static_cast<float>(s.options.get_number("q_scale", 1.0));
         m.k_scale = static_cast<float>(s.options.get_number("k_scale", 1.0));
         head_norm = s.options.get_bool("head_norm", true);
+        const std::string over = s.options.get_string("norm_over", "head");
+        if (over != "head" && over != "all") throw unsupported("matrix_memory: norm_over '{}' is not supported; supported: head, all", over);
+        norm_all = over == "all";
+        const std::string qkv_act = s.options.get_string("qkv_activation", "none");
+        if (qkv_act != "none") {
+            activation = kernels::gate_from_name(qkv_act);
+            if (activation > kernels::kRelu) throw unsupported("matrix_memory: qkv_activation '{}' is not supported; supported: none, sigmoid, silu, gelu_tanh, relu", qkv_act);
+        }
         eps = static_cast<float>(s.options.get_number("eps", 1e-6));
         gate = kernels::gate_from_name(s.options.get_string("gate", "silu"));
         proj = Linear(p, "proj.", "matrix_memory.proj");
@@ -263,8 +307,8 @@ public:
     static constexpr int kPiecesFrom = 128;
     kernels::MemoryShape m;
     int64_t hidden = 0;
-    bool gated = false, head_norm = true;
-    int gate = kernels::kSilu;
+    bool gated = false, head_norm = true, norm_all = false;
+    int gate = kernels::kSilu, activation = -1;
     float eps = 1e-6f;
     Linear proj, out;
     const float* norm_gain = nullptr;
@@ -283,6 +327,7 @@ private:
         const int64_t HD = static_cast<int64_t>(H) * D, HE = static_cast<int64_t>(H) * E;
         const Rows q = pr.columns(0, HD), k = pr.columns(HD, HD), v = pr.columns(2 * HD, HE), g = pr.columns(2 * HD + HE, HE);
         const Rows zi = pr.columns(gate_at(), H), zf = pr.columns(gate_at() + H, H);
+        if (activation >= 0) kernels::activate_columns(s, pr.columns(0, 2 * HD + HE), T, activation);
         const Rows o = ws.get("matrix_memory.o", T, HE, DType::F32);
         const float* decays = gated ? nullptr : decay.get(s);
         const float* freqs = m.rot_dims > 0 ? freq.get(s) : nullptr;
@@ -298,7 +343,8 @@ private:
         }
         ctx.tap("memory", o);
         const Rows heads = ws.get("matrix_memory.heads", T, HE, ctx.runtime.dtype);
-        kernels::head_gate(s, o, E, g, norm_gain, heads, T, H, E, head_norm, gate, eps);
+        if (norm_all) kernels::row_norm_gate(s, o, g, norm_gain, heads, T, gate, eps);
+        else kernels::head_gate(s, o, E, g, norm_gain, heads, T, H, E, head_norm, gate, eps);
         kernels::linear(ctx.runtime, &ws, heads, out.weight, nullptr, y, T, kernels::kNone, residual);
     }
     DeviceFloats decay, freq;
@@ -424,17 +470,23 @@ public:
         finish(ctx, gu, x);
         return true;
     }
+    void forward_into(StepContext& ctx, const Rows& h, const Rows& y) override {
+        const int T = ctx.n_tokens;
+        const Rows gu = ctx.workspace->get("gated.gate_up", T, 2 * inner, DType::F32);
+        gate_up.forward(ctx, h, gu, T);
+        finish(ctx, gu, y, false);
+    }
     int64_t inner;
     int gate;
     float alpha, limit;
     Linear gate_up, down;
 
 private:
-    void finish(StepContext& ctx, const Rows& gu, const Rows& x) {
+    void finish(StepContext& ctx, const Rows& gu, const Rows& x, bool add = true) {
         const int T = ctx.n_tokens;
         const Rows mid = ctx.workspace->get("gated.inner", T, inner, ctx.runtime.dtype);
         kernels::gated_act(ctx.stream(), gu, mid, T, gate, alpha, limit);
-        down.forward(ctx, mid, x, T, kernels::kNone, &x);
+        down.forward(ctx, mid, x, T, kernels::kNone, add ? &x : nullptr);
     }
 };
 
@@ -447,6 +499,8 @@ private:
 // feed-forward's (the capped form with `gate_alpha`, `gate_limit`).  With
 // `shared_inner` > 0 a gated feed-forward of that size runs for every row and is added.  The experts' matrices are stacked:
 // gate_up [experts x 2 inner, hidden] (per expert its gate rows, then its up rows) and down [experts x hidden, inner].
+// `route` "table": no router; the parameter `table` (int32 [vocab, top], a row's entries all different) names the experts of every token id,
+// each with the weight 1 / top.
 
 class RoutedExperts final : public FeedForward {
 public:
@@ -461,8 +515,12 @@ public:
         const std::string weight_on = s.options.get_string("weight_on", "input");
         if (weight_on != "input" && weight_on != "output") throw unsupported("routed: weight_on '{}' is not supported; supported: input, output", weight_on);
         weight_on_output = weight_on == "output";
-        router = p.at("router.weight");
-        if (s.options.get_bool("router_bias", false)) router_bias = f32_or_null(&p.at("router.bias"));
+        const std::string route = s.options.get_string("route", "scores");
+        if (route != "scores" && route != "table") throw unsupported("routed: route '{}' is not supported; supported: scores, table", route);
+        by_table = route == "table";
+        if (by_table) table = p.at("table");
+        else router = p.at("router.weight");
+        if (!by_table && s.options.get_bool("router_bias", false)) router_bias = f32_or_null(&p.at("router.bias"));
         gate_up = p.at("experts.gate_up.weight");
         down = p.at("experts.down.weight");
         if (s.options.get_int("shared_inner", 0) > 0) shared = std::make_unique<GatedFeedForward>(shared_spec(s), p.sub("shared."));
@@ -473,8 +531,13 @@ public:
     }
     static std::vector<ParamDecl> parameters(const PartSpec& s) {
         const int64_t hidden = need_int(s, "hidden"), inner = need_int(s, "inner"), E = need_int(s, "experts");
-        std::vector<ParamDecl> out{{"router.weight", {E, hidden}, ParamKind::Matrix}};
-        if (s.options.get_bool("router_bias", false)) out.push_back({"router.bias", {E}, ParamKind::Vector});
+        std::vector<ParamDecl> out;
+        if (s.options.get_string("route", "scores") == "table") {
+            out.push_back({"table", {need_int(s, "vocab"), need_int(s, "top")}, ParamKind::Index});
+        } else {
+            out.push_back({"router.weight", {E, hidden}, ParamKind::Matrix});
+            if (s.options.get_bool("router_bias", false)) out.push_back({"router.bias", {E}, ParamKind::Vector});
+        }
         for (ParamDecl d : std::vector<ParamDecl>{{"experts.gate_up.weight", {E * 2 * inner, hidden}, ParamKind::Matrix},
                                    {"experts.down.weight", {E * hidden, inner}, ParamKind::Matrix}})
             out.push_back(std::move(d));
@@ -493,7 +556,8 @@ public:
         int32_t* place = static_cast<int32_t*>(ws.get("routed.place", T, top, DType::I32).data);
         int32_t* pair_at = static_cast<int32_t*>(ws.get("routed.pair_at", T, top, DType::I32).data);
         int32_t* offsets = static_cast<int32_t*>(ws.flat("routed.offsets", experts + 1, DType::I32));
-        kernels::router_topk(s, h, router, ids, weights, T, top, softmax, renormalise, router_bias);
+        if (by_table) kernels::router_table(s, ctx.tokens, table, ids, weights, T, top, experts);
+        else kernels::router_topk(s, h, router, ids, weights, T, top, softmax, renormalise, router_bias);
         kernels::expert_plan(s, ids, pairs, experts, offsets, place, pair_at);
         Rows mid = ws.get("routed.inner", T, static_cast<int64_t>(top) * inner, ctx.runtime.dtype);
         mid = Rows{mid.data, mid.dtype, static_cast<int64_t>(pairs), inner, inner};
@@ -508,10 +572,10 @@ public:
     }
     int64_t hidden, inner;
     int experts, top, gate;
-    bool renormalise, softmax = false, weight_on_output = false;
+    bool renormalise, softmax = false, weight_on_output = false, by_table = false;
     float alpha, limit;
     const float* router_bias = nullptr;
-    Tensor router, gate_up, down;
+    Tensor router, table, gate_up, down;
     std::unique_ptr<GatedFeedForward> shared;
 };
 

@@ -22,10 +22,30 @@ int activation_from_name(const std::string& name) {
     if (name == "gelu_tanh") return kGeluTanh;
     if (name == "gelu_erf") return kGeluErf;
     if (name == "xielu") return kXielu;
-    throw unsupported("activation '{}' is not supported; supported: gelu_tanh, gelu_erf, xielu, none", name);
+    if (name == "relu2") return kRelu2;
+    throw unsupported("activation '{}' is not supported; supported: gelu_tanh, gelu_erf, xielu, relu2, none", name);
 }
 
 namespace {
+// Which of the bfloat16 attention kernels take a sink a head: 1 scalar decode, 2 tensor-core decode, 4 prefill on mma.sync, 8 prefill on tcgen05.
+constexpr int kSinkKernels = 0;
+// The latent attention's extras as the kernels take them; `gate`: one float a (token, head), or null.
+lb_latent_extras latent_extras(const LatentShape& a, const Rows* gate, bool with_sink = true, const Rows* latent = nullptr) {
+    lb_latent_extras x{};
+    x.sink = with_sink ? a.sink : nullptr;
+    if (gate != nullptr && gate->data != nullptr) {
+        if (gate->dtype != DType::F32 || gate->cols != a.n_head) throw invalid_argument("latent attention: the gate is one float a head");
+        x.gate = gate->f32();
+        x.ldg = gate->stride;
+    }
+    x.interleaved = a.interleaved ? 1 : 0;
+    if (latent != nullptr && latent->data != nullptr) {
+        if (latent->dtype != DType::F32 || latent->cols != a.rank + a.rot) throw invalid_argument("latent attention: the latent rows must be float32 [tokens, rank + rot]");
+        x.latent = latent->f32();
+        x.ldl = latent->stride;
+    }
+    return x;
+}
 int code(DType t, const char* what) {
     if (t == DType::F32) return 0;
     if (t == DType::BF16) return 1;
@@ -210,10 +230,11 @@ bool linear_with_cache(const Runtime& rt, Workspace* ws, const Rows& a, const Te
     return true;
 }
 
-bool decode_scalar_supports(const AttentionShape& a) { return lb_decode_attention_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
-bool decode_mma_supports(const AttentionShape& a) { return lb_decode_attention_mma_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
-bool prefill_supports(const AttentionShape& a) { return lb_prefill_attention_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
-bool prefill_tc_supports(const AttentionShape& a) { return lb_prefill_attention_tc_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
+// Heads with a sink run on the kernels that take one (kSinkKernels says which); the others decline such a shape.
+bool decode_scalar_supports(const AttentionShape& a) { return (a.sink == nullptr || (kSinkKernels & 1)) && lb_decode_attention_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
+bool decode_mma_supports(const AttentionShape& a) { return (a.sink == nullptr || (kSinkKernels & 2)) && lb_decode_attention_mma_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
+bool prefill_supports(const AttentionShape& a) { return (a.sink == nullptr || (kSinkKernels & 4)) && lb_prefill_attention_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
+bool prefill_tc_supports(const AttentionShape& a) { return (a.sink == nullptr || (kSinkKernels & 8)) && lb_prefill_attention_tc_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
 
 int decode_splits(int n_seq, int n_kv_head, int max_context, bool tensor_cores) {
     // How many ways each request's keys are split.  Scalar kernel: enough blocks for about four full waves of
@@ -235,9 +256,9 @@ void attention_generic(cudaStream_t s, DType dtype, const Rows& q, const void* c
                        const int32_t* positions, const int32_t* block_table, int table_width, const Rows& out, int n_tokens,
                        const AttentionShape& a) {
     if (q.dtype != dtype || out.dtype != dtype) throw invalid_argument("attention: q, cache and out must have one element type");
-    check(lb_paged_attention_generic_biased(code(dtype, "cache"), q.data, q.stride, cache, tok_seq, positions, block_table, table_width,
-                                     out.data, out.stride, n_tokens, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale,
-                                     a.mask(), a.distance, s), "paged_attention_generic");
+    check(lb_paged_attention_generic_sink(code(dtype, "cache"), q.data, q.stride, cache, tok_seq, positions, block_table, table_width,
+                                          out.data, out.stride, n_tokens, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale,
+                                          a.mask(), a.distance, a.sink, s), "paged_attention_generic");
 }
 
 void decode_attention(cudaStream_t s, bool tensor_cores, const Rows& q, const void* cache, int n_pages, const int32_t* positions,
@@ -328,6 +349,41 @@ void head_gate(cudaStream_t s, const Rows& o, int o_head, const Rows& g, const f
 void gated_act(cudaStream_t s, const Rows& gu, const Rows& mid, int n_rows, int gate, float alpha, float limit) {
     if (gu.dtype != DType::F32 || gu.cols != 2 * mid.cols) throw invalid_argument("gated_act: buffers do not fit");
     check(lb_gated_act_kind(code(mid.dtype, "mid"), gu.f32(), gu.stride, mid.data, mid.stride, n_rows, static_cast<int>(mid.cols), gate, alpha, limit, s), "gated_act");
+}
+
+void qkv_rotary_store(cudaStream_t s, const Rows& proj, const QkvColumns& c, const float* q_weight, const float* k_weight, const Rows& q_out, void* cache,
+                      const int32_t* slot_mapping, int n_tokens, int norm_mode, float eps, const int32_t* positions, const float* freq, int rot_dims,
+                      const Rows* v_first_in, const Rows* v_first_out, const float* lambda) {
+    if (proj.dtype != DType::F32 || q_out.cols != static_cast<int64_t>(c.n_head) * c.padded) throw invalid_argument("qkv_rotary_store: buffers do not fit");
+    const int64_t vcols = static_cast<int64_t>(c.n_kv_head) * c.vdim;
+    const Rows* shared = v_first_in != nullptr ? v_first_in : v_first_out;
+    if (shared != nullptr && (shared->dtype != DType::F32 || shared->cols != vcols || shared->rows < n_tokens))
+        throw invalid_argument("qkv_rotary_store: the shared values are float32 [tokens, {}]", vcols);
+    check(lb_qkv_rotary_store(code(q_out.dtype, "q_out"), proj.f32(), proj.stride, c.q_off, c.k_off, c.v_off, q_weight, k_weight, q_out.data, q_out.stride, cache,
+                              slot_mapping, n_tokens, c.n_head, c.n_kv_head, c.dim, c.vdim, c.padded, c.page_size, norm_mode, eps, positions, freq, rot_dims,
+                              v_first_in != nullptr ? v_first_in->f32() : nullptr, v_first_out != nullptr ? v_first_out->f32() : nullptr,
+                              shared != nullptr ? shared->stride : 0, lambda, s), "qkv_rotary_store");
+}
+
+void row_norm_gate(cudaStream_t s, const Rows& o, const Rows& g, const float* gain, const Rows& out, int n_rows, int gate, float eps) {
+    if (o.dtype != DType::F32 || out.cols != o.cols || (g.data != nullptr && (g.dtype != DType::F32 || g.cols != o.cols))) throw invalid_argument("row_norm_gate: buffers do not fit");
+    check(lb_row_norm_gate(code(out.dtype, "out"), o.f32(), o.stride, g.f32(), g.stride, gain, out.data, out.stride, n_rows, static_cast<int>(o.cols), gate, eps, s),
+          "row_norm_gate");
+}
+
+void activate_columns(cudaStream_t s, const Rows& x, int n_rows, int gate) {
+    if (x.dtype != DType::F32) throw invalid_argument("activate_columns: the rows are float32");
+    check(lb_activate_columns(x.f32(), x.stride, n_rows, static_cast<int>(x.cols), gate, s), "activate_columns");
+}
+
+void router_table(cudaStream_t s, const int32_t* tokens, const Tensor& table, int32_t* ids, float* weights, int n_rows, int top, int n_experts) {
+    if (table.dtype != DType::I32 || table.shape.size() != 2 || table.dim(1) != top) throw invalid_argument("router table: an int32 table [vocab, top]");
+    check(lb_router_table(tokens, static_cast<const int32_t*>(table.data), ids, weights, n_rows, top, n_experts, static_cast<int>(table.dim(0)), s), "router_table");
+}
+
+void rows_to_bf16(cudaStream_t s, const Rows& x, const Rows& y, int n_rows) {
+    if (x.dtype != DType::F32 || y.dtype != DType::BF16 || x.cols != y.cols) throw invalid_argument("rows_to_bf16: float32 rows into bfloat16 rows of the same width");
+    check(lb_rows_to_bf16(x.f32(), x.stride, y.data, y.stride, n_rows, static_cast<int>(x.cols), s), "rows_to_bf16");
 }
 
 int memory_value_tile(int dim, int vdim) {
@@ -459,15 +515,16 @@ void token_side(const Runtime& rt, Workspace* ws, const Rows& x, const int32_t* 
 void latent_store(cudaStream_t s, const Rows& d, const float* gain, const float* freq, const int32_t* positions, const int32_t* slot_mapping,
                   void* cache, DType cache_dtype, int n_tokens, const LatentShape& a, float eps) {
     if (d.dtype != DType::F32 || d.cols != a.rank + a.rot) throw invalid_argument("latent store: the rows must be float32 [tokens, rank + rot]");
-    check(lb_latent_store(code(cache_dtype, "cache"), d.f32(), d.stride, gain, freq, positions, slot_mapping, cache, n_tokens, a.rank, a.rot, a.rot_dims,
-                          eps, s), "latent_store");
+    const lb_latent_extras x = latent_extras(a, nullptr);
+    check(lb_latent_store_ext(code(cache_dtype, "cache"), d.f32(), d.stride, gain, freq, positions, slot_mapping, cache, n_tokens, a.rank, a.rot, a.rot_dims,
+                              eps, &x, s), "latent_store");
 }
 
 void rope_heads(cudaStream_t s, const Rows& q, const float* freq, const int32_t* positions, const Rows& wide, int n_tokens, const LatentShape& a) {
     if (wide.cols != static_cast<int64_t>(a.n_head) * (a.rank + a.rot) || q.cols != static_cast<int64_t>(a.n_head) * (a.dim + a.rot))
         throw invalid_argument("rotation of queries: buffers do not fit");
-    check(lb_rope_heads(code(q.dtype, "q"), code(wide.dtype, "wide"), q.data, q.stride, freq, positions, wide.data, wide.stride, n_tokens, a.n_head, a.dim,
-                        a.rot, a.rot_dims, a.rank, s), "rope_heads");
+    check(lb_rope_heads_ext(code(q.dtype, "q"), code(wide.dtype, "wide"), q.data, q.stride, freq, positions, wide.data, wide.stride, n_tokens, a.n_head, a.dim,
+                            a.rot, a.rot_dims, a.rank, a.interleaved ? 1 : 0, s), "rope_heads");
 }
 
 void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b, int64_t b_head, int64_t b_k, int64_t b_n, const Rows& c,
@@ -483,26 +540,29 @@ void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b,
 bool latent_few_supports(const LatentShape& a) { return lb_latent_few_supports(a.dim, a.rot, a.rank, a.vdim, 1) != 0; }
 
 void latent_prepare(cudaStream_t s, const Rows& qd, const Tensor& uk, const float* gain, const float* freq, const int32_t* positions,
-                    const int32_t* slot_mapping, void* cache, const Rows& wide, int n_tokens, const LatentShape& a, float eps) {
+                    const int32_t* slot_mapping, void* cache, const Rows& wide, int n_tokens, const LatentShape& a, float eps, const Rows* latent) {
     if (qd.dtype != DType::F32 || uk.dtype != DType::BF16 || wide.dtype != DType::BF16) throw invalid_argument("latent queries: float32 rows, bfloat16 map and wide queries");
-    check(lb_latent_prepare(qd.f32(), qd.stride, uk.data, gain, freq, positions, slot_mapping, cache, wide.data, wide.stride, n_tokens, a.n_head, a.dim, a.rot,
-                            a.rot_dims, a.rank, eps, s), "latent_prepare");
+    const lb_latent_extras x = latent_extras(a, nullptr, true, latent);
+    check(lb_latent_prepare_ext(qd.f32(), qd.stride, uk.data, gain, freq, positions, slot_mapping, cache, wide.data, wide.stride, n_tokens, a.n_head, a.dim,
+                                a.rot, a.rot_dims, a.rank, eps, &x, s), "latent_prepare");
 }
 
 void latent_finish(cudaStream_t s, const Rows& attended, const float* part_o, const float* part_ml, const Tensor& uv, const Rows& values, int n_tokens,
-                   const LatentShape& a, int n_splits) {
+                   const LatentShape& a, int n_splits, const Rows* gate) {
     if (attended.dtype != DType::F32 || uv.dtype != DType::BF16 || values.dtype != DType::BF16) throw invalid_argument("latent values: float32 latents, bfloat16 map and values");
-    check(lb_latent_finish(attended.f32(), attended.stride, part_o, part_ml, uv.data, values.data, values.stride, n_tokens, a.n_head, a.rank, a.vdim, n_splits, s),
-          "latent_finish");
+    const lb_latent_extras x = latent_extras(a, gate);
+    check(lb_latent_finish_ext(attended.f32(), attended.stride, part_o, part_ml, uv.data, values.data, values.stride, n_tokens, a.n_head, a.rank, a.vdim, n_splits,
+                               &x, s), "latent_finish");
 }
 
 bool latent_rows_supports(const LatentShape& a) { return lb_latent_attention_rows_supports(a.n_head, a.rank, a.rot, a.page_size) != 0; }
 
 void latent_attention_rows16(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
-                             int table_width, const Rows& out, int n_tokens, int n_seq, int max_q_len, const LatentShape& a) {
+                             int table_width, const Rows& out, int n_tokens, int n_seq, int max_q_len, const LatentShape& a, const Rows* gate) {
     if (wide.dtype != DType::BF16 || out.dtype != DType::BF16) throw invalid_argument("latent attention, 64 rows a block: bfloat16 wide queries and attended latents");
-    check(lb_latent_attention_rows16(wide.data, wide.stride, cache, q_start, n_past, block_table, table_width, out.data, out.stride, n_tokens, n_seq, max_q_len,
-                                     a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, s), "latent_attention_rows16");
+    const lb_latent_extras x = latent_extras(a, gate);
+    check(lb_latent_attention_rows16_ext(wide.data, wide.stride, cache, q_start, n_past, block_table, table_width, out.data, out.stride, n_tokens, n_seq, max_q_len,
+                                         a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, &x, s), "latent_attention_rows16");
 }
 
 bool latent_mma_supports(const LatentShape& a) { return lb_latent_attention_mma_supports(a.n_head, a.rank, a.rot, a.page_size) != 0; }
@@ -515,18 +575,21 @@ int latent_splits(int n_seq, int n_head, int span) {
 
 void latent_attention_mma(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
                           int table_width, const Rows& out, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, const LatentShape& a,
-                          int n_splits, bool merge) {
+                          int n_splits, bool merge, const Rows* gate) {
     if (wide.dtype != DType::BF16 || out.dtype != DType::F32) throw invalid_argument("latent attention on tensor cores: bfloat16 wide queries, float32 attended latents");
-    check(lb_latent_attention_mma(wide.data, wide.stride, cache, q_start, n_past, block_table, table_width, out.f32(), out.stride, part_o, part_ml, n_tokens, n_seq,
-                                  max_q_len, a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, n_splits, merge ? 1 : 0, s), "latent_attention_mma");
+    const lb_latent_extras x = latent_extras(a, gate);
+    check(lb_latent_attention_mma_ext(wide.data, wide.stride, cache, q_start, n_past, block_table, table_width, out.f32(), out.stride, part_o, part_ml, n_tokens,
+                                      n_seq, max_q_len, a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, n_splits, merge ? 1 : 0, &x, s),
+          "latent_attention_mma");
     if (n_splits > 1 && merge) launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,
-                      const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a) {
+                      const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a, const Rows* gate) {
     if (wide.dtype != DType::F32 || out.dtype != DType::F32) throw invalid_argument("latent attention: wide queries and attended latents are float32");
-    check(lb_latent_attention(code(cache_dtype, "cache"), wide.f32(), wide.stride, cache, tok_seq, positions, block_table, table_width, out.f32(),
-                              out.stride, n_tokens, a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, s), "latent_attention");
+    const lb_latent_extras x = latent_extras(a, gate);
+    check(lb_latent_attention_ext(code(cache_dtype, "cache"), wide.f32(), wide.stride, cache, tok_seq, positions, block_table, table_width, out.f32(),
+                                  out.stride, n_tokens, a.n_head, a.rank, a.rot, a.page_size, a.scale, a.window, &x, s), "latent_attention");
 }
 
 void sample(cudaStream_t s, const float* logits, int64_t row_stride, int n_rows, int vocab, const float* temperature,

@@ -24,7 +24,7 @@ extern std::atomic<uint64_t> launches;
 void check(int status, const char* what);
 
 // kXielu: the activation's two learned numbers ride behind the bias (a bias of N + 2 floats: bias[N] = p, bias[N + 1] = q).
-enum Activation : int { kNone = 0, kGeluTanh = 1, kGeluErf = 2, kXielu = 3 };
+enum Activation : int { kNone = 0, kGeluTanh = 1, kGeluErf = 2, kXielu = 3, kRelu2 = 4 };      // kRelu2: max(z, 0)^2
 int activation_from_name(const std::string& name);      // UNSUPPORTED when unknown
 
 // Keys and values of a fused projection that go straight to a layer's cache pages.
@@ -91,6 +91,8 @@ struct AttentionShape {
     int chunk = 0;           // c > 0: a query sees the earlier keys of its own chunk of c positions, counted from position 0
     // A penalty by distance: device floats r1 [n_head] then r2 [n_head]; the score of the key d positions back loses r1 ln(1 + r2 d).
     const float* distance = nullptr;
+    // A sink a head: device floats [n_head]; exp(sink[h]) joins the divisor of the head's softmax as it is, with no key and no value.
+    const float* sink = nullptr;
     // One number for the kernels: 0 all earlier keys, w > 0 a window, -c a chunk (a shape has one of the two at most).
     int mask() const { return chunk > 0 ? -chunk : window; }
 };
@@ -139,6 +141,8 @@ struct LatentShape {
     int n_head = 0, dim = 0, rot = 0, rot_dims = 0, vdim = 0, rank = 0, page_size = 0;
     float scale = 1.0f;
     int window = 0;
+    const float* sink = nullptr;     // device floats [n_head]: exp(sink[h]) joins the divisor of the head's softmax (no key, no value)
+    bool interleaved = false;        // the rotation pairs value 2i with 2i + 1 instead of i with i + rot_dims / 2
 };
 void latent_store(cudaStream_t s, const Rows& d, const float* gain, const float* freq, const int32_t* positions, const int32_t* slot_mapping,
                   void* cache, DType cache_dtype, int n_tokens, const LatentShape& a, float eps);
@@ -150,22 +154,23 @@ void head_matmul(cudaStream_t s, const Rows& a, int64_t a_head, const Tensor& b,
 // Steps of few tokens in bfloat16: rotation, keys' map and cache row in one launch; merge of the attention's parts and values' map in one.
 bool latent_few_supports(const LatentShape& a);
 void latent_prepare(cudaStream_t s, const Rows& qd, const Tensor& uk, const float* gain, const float* freq, const int32_t* positions,
-                    const int32_t* slot_mapping, void* cache, const Rows& wide, int n_tokens, const LatentShape& a, float eps);
+                    const int32_t* slot_mapping, void* cache, const Rows& wide, int n_tokens, const LatentShape& a, float eps,
+                    const Rows* latent = nullptr);      // latent: the rows [latent | rotated key] where they do not follow the queries in qd
 void latent_finish(cudaStream_t s, const Rows& attended, const float* part_o, const float* part_ml, const Tensor& uv, const Rows& values, int n_tokens,
-                   const LatentShape& a, int n_splits);
+                   const LatentShape& a, int n_splits, const Rows* gate = nullptr);      // gate: one float a (token, head); the head's values times its sigmoid
 // The tensor-core kernel (bfloat16 wide queries and cache): whether it takes the shape, into how many parts a decode step's keys are cut
 // (a function of the step's shape and the longest span a query can see, so a recorded step and an eager one cut alike), and the launch.
 bool latent_mma_supports(const LatentShape& a);
 // Runs of tokens, latents of up to 256 values: 64 rows a block, the attended latents out as bfloat16 for the values' product.
 bool latent_rows_supports(const LatentShape& a);
 void latent_attention_rows16(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
-                             int table_width, const Rows& out, int n_tokens, int n_seq, int max_q_len, const LatentShape& a);
+                             int table_width, const Rows& out, int n_tokens, int n_seq, int max_q_len, const LatentShape& a, const Rows* gate = nullptr);
 int latent_splits(int n_seq, int n_head, int span);
 void latent_attention_mma(cudaStream_t s, const Rows& wide, const void* cache, const int32_t* q_start, const int32_t* n_past, const int32_t* block_table,
                           int table_width, const Rows& out, float* part_o, float* part_ml, int n_tokens, int n_seq, int max_q_len, const LatentShape& a,
-                          int n_splits, bool merge = true);       // merge false: the parts are left for latent_finish
+                          int n_splits, bool merge = true, const Rows* gate = nullptr);       // merge false: the parts are left for latent_finish
 void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const void* cache, const int32_t* tok_seq, const int32_t* positions,
-                      const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a);
+                      const int32_t* block_table, int table_width, const Rows& out, int n_tokens, const LatentShape& a, const Rows* gate = nullptr);
 
 // ---- pieces around gated mixers and mixers of several branches ----
 // x[r, :] += v (float [width]) for the first n_rows rows.
@@ -181,6 +186,20 @@ struct QkvColumns {
 void qk_norm_store(cudaStream_t s, const Rows& proj, const QkvColumns& c, const float* q_weight, const float* k_weight, const Rows& q_out, void* cache,
                    const int32_t* slot_mapping, int n_tokens, bool norm, float eps, const int32_t* positions = nullptr, float temp_coef = 0.0f,
                    int temp_every = 0);
+// The same for queries and keys that are normed over the whole projection and rotated, and for values that blend with an earlier layer's:
+// norm_mode 0 none, 1 a head (gains [dim]), 2 all of q and all of k each over one root mean square (gains [n_head * dim], [n_kv_head * dim]);
+// the first rot_dims values of a head rotated in pairs (i, i + rot_dims / 2) by positions[t] * freq[i]; with v_first_in the values become
+// (1 - lambda) v + lambda v_first_in[t], with v_first_out the row's own values are left there (float [T, n_kv_head * vdim]).
+void qkv_rotary_store(cudaStream_t s, const Rows& proj, const QkvColumns& c, const float* q_weight, const float* k_weight, const Rows& q_out, void* cache,
+                      const int32_t* slot_mapping, int n_tokens, int norm_mode, float eps, const int32_t* positions, const float* freq, int rot_dims,
+                      const Rows* v_first_in, const Rows* v_first_out, const float* lambda);
+// out = o over the root mean square of the whole row, times gain (or null), times gate(g) (rows g without data: no gate).
+void row_norm_gate(cudaStream_t s, const Rows& o, const Rows& g, const float* gain, const Rows& out, int n_rows, int gate, float eps);
+// In place over the float rows x[:n_rows]: sigmoid, silu, gelu_tanh or relu (a Gate code).
+void activate_columns(cudaStream_t s, const Rows& x, int n_rows, int gate);
+// A row's experts looked up by its token id in an int32 table [vocab, top]; every weight 1 / top.
+void router_table(cudaStream_t s, const int32_t* tokens, const Tensor& table, int32_t* ids, float* weights, int n_rows, int top, int n_experts);
+void rows_to_bf16(cudaStream_t s, const Rows& x, const Rows& y, int n_rows);
 // kCapped has two numbers (alpha, limit): g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1).
 enum Gate : int { kSigmoid = 0, kSilu = 1, kGeluGate = 2, kRelu = 3, kCapped = 4 };
 int gate_from_name(const std::string& name);

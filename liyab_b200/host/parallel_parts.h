@@ -80,6 +80,11 @@ private:
 // of the rot_dim values (value i pairs with i + rot_dims/2; angle = position * base^(-2i/rot_dims)).  `window` w > 0:
 // position i sees j with 0 <= i - j < w.  With `own_latent` false the part has no down projection and reads the rows
 // that another run of the model wrote (the run order names it); its window, heads and maps are its own.
+// Further options.  `q_rank` r > 0: the queries come through a latent of their own, q = q_up (rms_norm(q_down h) * q_norm.weight); the down
+// map is part of the one projection.  `rot_layout` "interleaved": the rotation pairs value 2i with 2i + 1 instead of i with i + rot_dims/2.
+// `sink`: a learned number a head (the parameter `sink`) whose exponential joins the divisor of the head's softmax; no key, no value, not
+// scaled.  `head_gate`: the projection also makes one number a head, and the head's result is multiplied by its sigmoid.
+// The projection's rows: [queries or their latent | latent row (with own_latent) | gates (with head_gate)].
 
 class LatentAttention final : public Mixer {
 public:
@@ -95,6 +100,12 @@ public:
         a.scale = static_cast<float>(s.options.get_number("scale", 1.0 / std::sqrt(static_cast<double>(a.dim + a.rot))));
         eps = static_cast<float>(s.options.get_number("eps", 1e-6));
         own_latent = s.options.get_bool("own_latent", true);
+        q_rank = s.options.get_int("q_rank", 0);
+        if (q_rank < 0) throw invalid_model("latent_attention: q_rank {} is negative", q_rank);
+        const std::string layout = s.options.get_string("rot_layout", "half");
+        if (layout != "half" && layout != "interleaved") throw unsupported("latent_attention: rot_layout '{}' is not supported; supported: half, interleaved", layout);
+        a.interleaved = layout == "interleaved";
+        head_gate = s.options.get_bool("head_gate", false);
         if (a.rot_dims < 0 || a.rot_dims > a.rot || a.rot_dims % 2 != 0)
             throw invalid_model("latent_attention: {} of {} rotated values cannot be rotated in pairs", a.rot_dims, a.rot);
         if (a.window < 0) throw invalid_model("latent_attention: window {} is negative", a.window);
@@ -107,14 +118,26 @@ public:
         uk = p.at("uk.weight");
         uv = p.at("uv.weight");
         if (own_latent) latent_gain = f32_or_null(&p.at("latent_norm.weight"));
+        if (q_rank > 0) {
+            q_gain = f32_or_null(&p.at("q_norm.weight"));
+            q_up = Linear(p, "q_up.", "latent_attention.q_up");
+        }
+        if (s.options.get_bool("sink", false)) a.sink = f32_or_null(&p.at("sink"));
     }
     static std::vector<ParamDecl> parameters(const PartSpec& s) {
         const int64_t hidden = need_int(s, "hidden"), H = need_int(s, "n_head"), dim = need_int(s, "dim", 0), rot = need_int(s, "rot_dim", 0);
         const int64_t vdim = need_int(s, "vdim"), rank = need_int(s, "kv_rank");
-        const bool own = s.options.get_bool("own_latent", true);
+        const bool own = s.options.get_bool("own_latent", true), gated = s.options.get_bool("head_gate", false);
+        const int64_t q_rank = s.options.get_int("q_rank", 0);
         std::vector<ParamDecl> out;
-        // One projection makes the queries and, where the part has a latent of its own, the row [latent | rotated key] behind them.
-        Linear::declare(out, "proj.", H * (dim + rot) + (own ? rank + rot : 0), hidden, false);
+        // One projection makes the queries (or their latent) and, where the part has a latent of its own, the row [latent | rotated key] behind
+        // them, then the heads' gates.
+        Linear::declare(out, "proj.", (q_rank > 0 ? q_rank : H * (dim + rot)) + (own ? rank + rot : 0) + (gated ? H : 0), hidden, false);
+        if (q_rank > 0) {
+            out.push_back({"q_norm.weight", {q_rank}, ParamKind::Vector});
+            Linear::declare(out, "q_up.", H * (dim + rot), q_rank, false);
+        }
+        if (s.options.get_bool("sink", false)) out.push_back({"sink", {H}, ParamKind::Vector});
         if (own) out.push_back({"latent_norm.weight", {rank}, ParamKind::Vector});
         out.push_back({"uk.weight", {H * dim, rank}, ParamKind::Matrix});
         out.push_back({"uv.weight", {H * vdim, rank}, ParamKind::Matrix});
@@ -124,7 +147,10 @@ public:
     bool capturable() const override { return true; }
     std::optional<KvNeed> kv_need() const override { return KvNeed{1, a.rank + a.rot, a.window, 1}; }
 
-    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override {
+    void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override { run(ctx, h, x, &x, unit); }
+    void forward_into(StepContext& ctx, const Rows& h, const Rows& y, CacheUnit unit) override { run(ctx, h, y, nullptr, unit); }
+
+    void run(StepContext& ctx, const Rows& h, const Rows& y, const Rows* residual, CacheUnit unit) {
         if (unit.write != own_latent)
             throw invalid_model("latent_attention: a part with a latent of its own writes its cache unit, one without reads another run's; the run order says otherwise");
         const int T = ctx.n_tokens;
@@ -138,18 +164,30 @@ public:
         shape.page_size = view->group->page_size;
         const int D = a.rank + a.rot;
         // Queries (and this step's cache rows) in 32-bit: the norm of the latent and both rotations read them.
-        const Rows qd = ws.get(own_latent ? "latent.qd" : "latent.q", T, q_cols + (own_latent ? D : 0), DType::F32);
+        const int64_t first_cols = q_rank > 0 ? q_rank : q_cols;
+        const Rows qd = ws.get(own_latent ? "latent.qd" : "latent.q", T, proj.weight.dim(0), DType::F32);
         proj.forward(ctx, h, qd, T);
-        const Rows q = qd.columns(0, q_cols);
+        const Rows row = own_latent ? qd.columns(first_cols, D) : Rows{};
+        const Rows gates = head_gate ? qd.columns(first_cols + (own_latent ? D : 0), a.n_head) : Rows{};
+        const Rows* gate = head_gate ? &gates : nullptr;
+        Rows q = qd.columns(0, q_cols);
+        if (q_rank > 0) {
+            // The queries' own latent: normed in 32-bit, then up to the heads.
+            const Rows cq = ws.get("latent.cq", T, q_rank, dt);
+            kernels::rms_groups(s, qd.columns(0, q_rank), nullptr, q_gain, cq, T, 1, eps);
+            q = ws.get("latent.q_up", T, q_cols, DType::F32);
+            q_up.forward(ctx, cq, q, T);
+        }
         // bfloat16 and a shape the tensor-core kernel takes: wide queries in bfloat16 for it; else 32-bit throughout.
         const bool tensor = dt == DType::BF16 && kernels::latent_mma_supports(shape);
         // Steps of few tokens are bound by their launches: one launch before the attention, one after it.
         const bool few = tensor && T <= kFewTokens && kernels::latent_few_supports(shape);
         const Rows wide = ws.get(tensor ? "latent.wide16" : "latent.wide", T, static_cast<int64_t>(a.n_head) * D, tensor ? DType::BF16 : DType::F32);
         if (few) {
-            kernels::latent_prepare(s, qd, uk, latent_gain, freq, ctx.positions, view->slot_mapping, own_latent ? cache : nullptr, wide, T, shape, eps);
+            kernels::latent_prepare(s, q, uk, latent_gain, freq, ctx.positions, view->slot_mapping, own_latent ? cache : nullptr, wide, T, shape, eps,
+                                    own_latent ? &row : nullptr);
         } else {
-            if (own_latent) kernels::latent_store(s, qd.columns(q_cols, D), latent_gain, freq, ctx.positions, view->slot_mapping, cache, dt, T, shape, eps);
+            if (own_latent) kernels::latent_store(s, row, latent_gain, freq, ctx.positions, view->slot_mapping, cache, dt, T, shape, eps);
             kernels::rope_heads(s, q, freq, ctx.positions, wide, T, shape);
             if (a.dim > 0)
                 kernels::head_matmul(s, q, a.dim + a.rot, uk, static_cast<int64_t>(a.dim) * a.rank, a.rank, 1, wide, D, T, a.rank, a.dim, a.n_head);
@@ -163,9 +201,10 @@ public:
         const Rows attended = rows16 ? ws.get("latent.attended16", T, static_cast<int64_t>(a.n_head) * a.rank, DType::BF16)
                                      : ws.get("latent.attended", T, static_cast<int64_t>(a.n_head) * a.rank, DType::F32);
         const Rows values = ws.get("latent.values", T, static_cast<int64_t>(a.n_head) * a.vdim, dt);
+        // A head's gate is one factor on everything the head puts out, so it acts where the softmax is divided (the values' map is linear).
         if (rows16) {
             kernels::latent_attention_rows16(s, wide, cache, ctx.q_start, ctx.n_past, view->block_table, view->table_width, attended, T, ctx.n_seq,
-                                             ctx.max_q_len, shape);
+                                             ctx.max_q_len, shape, gate);
         } else if (tensor) {
             // A decode step's keys are cut over several blocks so that a few requests still fill the GPU.
             const int span = a.window > 0 ? std::min(a.window, ctx.max_positions) : ctx.max_positions;
@@ -175,23 +214,26 @@ public:
                 part_o = static_cast<float*>(ws.flat("latent.part", static_cast<int64_t>(splits) * T * a.n_head * a.rank, DType::F32));
                 part_ml = static_cast<float*>(ws.flat("latent.part_ml", static_cast<int64_t>(splits) * T * a.n_head * 2, DType::F32));
             }
+            // Few tokens: the launch after the attention merges the parts and applies the gate; the sink acts where the parts meet, or in
+            // the attention itself when the keys are not split.
             kernels::latent_attention_mma(s, wide, cache, ctx.q_start, ctx.n_past, view->block_table, view->table_width, attended, part_o, part_ml, T,
-                                          ctx.n_seq, ctx.max_q_len, shape, splits, !few);
-            if (few) kernels::latent_finish(s, attended, part_o, part_ml, uv, values, T, shape, splits);
+                                          ctx.n_seq, ctx.max_q_len, shape, splits, !few, few ? nullptr : gate);
+            if (few) kernels::latent_finish(s, attended, part_o, part_ml, uv, values, T, shape, splits, gate);
         } else {
-            kernels::latent_attention(s, dt, wide, cache, ctx.tok_seq, ctx.positions, view->block_table, view->table_width, attended, T, shape);
+            kernels::latent_attention(s, dt, wide, cache, ctx.tok_seq, ctx.positions, view->block_table, view->table_width, attended, T, shape, gate);
         }
         if (!few) kernels::head_matmul(s, attended, a.rank, uv, static_cast<int64_t>(a.vdim) * a.rank, 1, a.rank, values, a.vdim, T, a.vdim, a.rank, a.n_head);
         ctx.tap("attention", values);
-        out.forward(ctx, values, x, T, kernels::kNone, &x);
+        out.forward(ctx, values, y, T, kernels::kNone, residual);
     }
 
     static constexpr int kFewTokens = 64;
     kernels::LatentShape a;
-    int64_t hidden = 0, q_cols = 0;
+    int64_t hidden = 0, q_cols = 0, q_rank = 0;
     float eps = 1e-6f;
-    bool own_latent = true;
-    Linear proj, out;
+    bool own_latent = true, head_gate = false;
+    Linear proj, out, q_up;
+    const float* q_gain = nullptr;
     Tensor uk, uv;
     const float* latent_gain = nullptr;
     std::vector<float> freq_host;

@@ -48,6 +48,12 @@ void Mixer::forward_into(StepContext& ctx, const Rows& h, const Rows& out, Cache
     forward(ctx, h, out, unit);
 }
 
+void FeedForward::forward_into(StepContext& ctx, const Rows& h, const Rows& out) {
+    LIYAB_CUDA(cudaMemset2DAsync(out.data, static_cast<size_t>(out.stride) * dtype_size(out.dtype), 0, static_cast<size_t>(out.cols) * dtype_size(out.dtype),
+                                 static_cast<size_t>(ctx.n_tokens), ctx.stream()));
+    forward(ctx, h, out);
+}
+
 const char* phase_name(Phase p) {
     static const char* names[] = {"embed", "norm", "mixer", "feed_forward", "head"};
     return names[static_cast<int>(p) % 5];

@@ -188,6 +188,9 @@ public:
 class FeedForward : public Part {
 public:
     virtual void forward(StepContext& ctx, const Rows& h, const Rows& x) = 0;
+    // Writes the feed-forward's output to `out` (float32 [T, width]) instead of adding it to the stream, for an arrangement that
+    // treats the output before it joins the stream.  By default `out` is cleared and `forward` adds into it.
+    virtual void forward_into(StepContext& ctx, const Rows& h, const Rows& out);
     // As Mixer::forward_from.
     virtual bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x) { return false; }
 };
