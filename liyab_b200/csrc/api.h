@@ -424,6 +424,25 @@ int lb_paged_attention_generic_sink(int dtype, const void* q, int64_t q_stride, 
                                     int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance, const float* sink,
                                     void* stream);
 
+/* The bfloat16 attention kernels with a sink a head (`sink` [n_head] or null, as lb_paged_attention_generic_sink's): it joins the divisor once,
+ * where a row's keys (or a request's key ranges) have all been summed. */
+int lb_decode_attention_sink(const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
+                             int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
+                             int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits, const float* distance,
+                             const float* sink, void* stream);
+int lb_decode_attention_mma_sink(const void* q, int64_t q_stride, const void* cache, int n_pages, const int32_t* positions,
+                                 const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial, int* counters,
+                                 int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits,
+                                 const float* distance, const float* sink, void* stream);
+int lb_prefill_attention_sink(const void* q, int64_t q_stride, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                              const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len,
+                              int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance,
+                              const float* sink, void* stream);
+int lb_prefill_attention_tc_sink(const void* q, int64_t q_stride, int n_tokens, const void* cache, int n_pages, const int32_t* q_start,
+                                 const int32_t* n_past, const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
+                                 int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window,
+                                 const float* distance, const float* sink, void* stream);
+
 /* What attention over latent rows may have besides its sizes.  sink [n_head]: exp(sink[h]) joins the divisor of head h's softmax (no key, no
  * value, not scaled).  gate: one float a (token, head) at gate[t * ldg + h]; the head's result is multiplied by sigmoid of it.  interleaved:
  * the rotation pairs value 2i with 2i + 1 instead of i with i + rot_dims / 2.  latent (lb_latent_prepare_ext): the rows [latent | rotated key],

@@ -59,7 +59,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
                         const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride,
                         __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ partial,
                         int* __restrict__ counters, int n_kv_head, int page_shift, float scale, int window, int n_splits,
-                        const float* __restrict__ distance) {
+                        const float* __restrict__ distance, const float* __restrict__ sink) {
     constexpr int TPK = HD / 8;                 // threads that share a key
     constexpr int KPW = 32 / TPK;               // keys a warp covers with one load
     constexpr int STATE = HD + 2;               // m, l, values
@@ -197,6 +197,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
             a += red[w][g][2 + d] * f;
         }
         if (n_splits == 1) {
+            if (sink != nullptr) a *= lb_sink_join_exp2(sink[kvh * G + g] * kLbLog2e, mm, ll);
             out[(size_t)seq * out_stride + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(a / ll);
         } else {
             my_partial[g * STATE + 2 + d] = a;
@@ -229,6 +230,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
             ll += __ldcg(st + 1) * f;
             a += __ldcg(st + 2 + d) * f;
         }
+        if (sink != nullptr) a *= lb_sink_join_exp2(sink[kvh * G + g] * kLbLog2e, mm, ll);      // once, where the ranges meet
         out[(size_t)seq * out_stride + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(a / ll);
     }
 }
@@ -236,11 +238,11 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
 template <int HD, int G>
 int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
            int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_kv_head,
-           int page_shift, float scale, int window, int n_splits, const float* distance, cudaStream_t s) {
+           int page_shift, float scale, int window, int n_splits, const float* distance, const float* sink, cudaStream_t s) {
     dim3 grid(n_splits, n_kv_head, n_seq);
     LB_CHECK_CUDA(lb_launch_overlapped(decode_attention_kernel<HD, G>, dim3(grid), dim3(kThreads), 0, s, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
-        (__nv_bfloat16*)out, out_stride, partial, counters, n_kv_head, page_shift, scale, window, n_splits, distance));
+        (__nv_bfloat16*)out, out_stride, partial, counters, n_kv_head, page_shift, scale, window, n_splits, distance, sink));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
@@ -248,10 +250,10 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* po
 template <int HD>
 int by_group(int group, const void* q, int64_t q_stride, const void* cache, const int32_t* positions,
              const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial, int* counters,
-             int n_seq, int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, cudaStream_t s) {
+             int n_seq, int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, const float* sink, cudaStream_t s) {
 #define LB_GO(G)                                                                                                   \
     return launch<HD, G>(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, \
-                         n_seq, n_kv_head, page_shift, scale, window, n_splits, distance, s)
+                         n_seq, n_kv_head, page_shift, scale, window, n_splits, distance, sink, s)
     switch (group) {
         case 1: LB_GO(1);
         case 2: LB_GO(2);
@@ -290,6 +292,14 @@ extern "C" int lb_decode_attention_biased(const void* q, int64_t q_stride, const
                                           int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
                                           int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits, const float* distance,
                                           void* stream) {
+    return lb_decode_attention_sink(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, n_seq, n_head, n_kv_head,
+                                    head_dim, page_size, scale, window, n_splits, distance, nullptr, stream);
+}
+
+extern "C" int lb_decode_attention_sink(const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
+                                        int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
+                                        int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits, const float* distance,
+                                        const float* sink, void* stream) {
     LB_CHECK_ARG(n_seq >= 0 && n_splits >= 1, "decode attention: bad sizes n_seq=%d n_splits=%d", n_seq, n_splits);
     if (!lb_decode_attention_supports(n_head, n_kv_head, head_dim, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "decode attention: unsupported shape heads %d/%d head_dim %d page_size %d", n_head,
@@ -303,7 +313,7 @@ extern "C" int lb_decode_attention_biased(const void* q, int64_t q_stride, const
     auto s = static_cast<cudaStream_t>(stream);
 #define LB_HD(HD)                                                                                                     \
     return by_group<HD>(group, q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, \
-                        n_seq, n_kv_head, page_shift, scale, window, n_splits, distance, s)
+                        n_seq, n_kv_head, page_shift, scale, window, n_splits, distance, sink, s)
     switch (head_dim) {
         case 16: LB_HD(16);
         case 32: LB_HD(32);

@@ -74,7 +74,7 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
                             const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride,
                             __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ partial,
                             int* __restrict__ counters, int n_head, int n_kv_head, int page_shift, float scale, int window,
-                            int n_splits, int cluster_merge, const float* __restrict__ distance) {
+                            int n_splits, int cluster_merge, const float* __restrict__ distance, const float* __restrict__ sink) {
     constexpr int kThreads = kWarps * 32;
     constexpr int LD = HD;                      // a tile's row in shared memory; its 16-byte chunks are XOR-swizzled by the row
     constexpr int CH = HD / 8;                  // 16-byte chunks per row
@@ -334,6 +334,7 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
             a += st[2 + d] * f;
         }
         if (n_splits == 1) {
+            if (sink != nullptr) a *= lb_sink_join_exp2(sink[kvh * G + r] * kLbLog2e, mm, ll);
             out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(a / ll);
         } else if (cluster_merge) {
             const uint32_t at = first_block + (uint32_t)(r * STATE) * 4u;
@@ -370,6 +371,7 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
                 ll += st[1] * f;
                 a += st[2 + d] * f;
             }
+            if (sink != nullptr) a *= lb_sink_join_exp2(sink[kvh * G + r] * kLbLog2e, mm, ll);      // once, where the ranges meet
             out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(a / ll);
         }
         return;
@@ -396,6 +398,7 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
             ll += __ldcg(st + 1) * f;
             a += __ldcg(st + 2 + d) * f;
         }
+        if (sink != nullptr) a *= lb_sink_join_exp2(sink[kvh * G + r] * kLbLog2e, mm, ll);      // once, where the ranges meet
         out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(a / ll);
     }
 }
@@ -431,7 +434,7 @@ struct Variant {
 
     static int launch(const CUtensorMap& map_kv, int kv_rows, int* status, const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
                       int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
-                      int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, cudaStream_t s) {
+                      int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, const float* sink, cudaStream_t s) {
         dim3 grid(n_splits, n_kv_head, n_seq);
         // Two to eight key ranges: the ranges of a request and head form a cluster and merge in shared memory.
         const int group = n_head / n_kv_head;
@@ -444,7 +447,7 @@ struct Variant {
                                                    dim3(kWarps * 32), smem + inbox, s, map_kv, kv_rows, status, (const __nv_bfloat16*)q,
                                                    q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
                                                    (__nv_bfloat16*)out, out_stride, partial, counters, n_head, n_kv_head, page_shift,
-                                                   scale, window, n_splits, cluster ? 1 : 0, distance));
+                                                   scale, window, n_splits, cluster ? 1 : 0, distance, sink));
         return LB_OK;
     }
 };
@@ -456,7 +459,7 @@ struct Variant {
 template <int HD, bool TMA>
 int launch_for(const CUtensorMap& map_kv, int kv_rows, int* status, const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
                int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
-               int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, cudaStream_t s) {
+               int n_kv_head, int page_shift, float scale, int window, int n_splits, const float* distance, const float* sink, cudaStream_t s) {
     using Wide = Variant<HD, 4, 2, TMA>;
     using Narrow = Variant<HD, 2, 2, TMA>;
     static int n_sm = 0;
@@ -475,9 +478,9 @@ int launch_for(const CUtensorMap& map_kv, int kv_rows, int* status, const void* 
     const bool narrow = blocks > slots_wide && waves_wide * slots_wide >= waves_narrow * slots_narrow;
     if (narrow)
         return Narrow::launch(map_kv, kv_rows, status, q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters,
-                              n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, s);
+                              n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, sink, s);
     return Wide::launch(map_kv, kv_rows, status, q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, n_seq,
-                        n_head, n_kv_head, page_shift, scale, window, n_splits, distance, s);
+                        n_head, n_kv_head, page_shift, scale, window, n_splits, distance, sink, s);
 }
 
 }  // namespace
@@ -504,6 +507,14 @@ extern "C" int lb_decode_attention_mma_biased(const void* q, int64_t q_stride, c
                                               const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial, int* counters,
                                               int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits,
                                               const float* distance, void* stream) {
+    return lb_decode_attention_mma_sink(q, q_stride, cache, n_pages, positions, block_table, table_stride, out, out_stride, partial, counters, n_seq, n_head,
+                                        n_kv_head, head_dim, page_size, scale, window, n_splits, distance, nullptr, stream);
+}
+
+extern "C" int lb_decode_attention_mma_sink(const void* q, int64_t q_stride, const void* cache, int n_pages, const int32_t* positions,
+                                            const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial, int* counters,
+                                            int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, int n_splits,
+                                            const float* distance, const float* sink, void* stream) {
     LB_CHECK_ARG(n_seq >= 0 && n_splits >= 1, "decode attention: bad sizes n_seq=%d n_splits=%d", n_seq, n_splits);
     if (!lb_decode_attention_mma_supports(n_head, n_kv_head, head_dim, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "decode attention (tensor cores): unsupported shape heads %d/%d head_dim %d page_size %d",
@@ -527,11 +538,11 @@ extern "C" int lb_decode_attention_mma_biased(const void* q, int64_t q_stride, c
             if (rc != LB_OK) return rc;
             return launch_for<64, true>(map_kv, (int)kv_rows, status, q, q_stride, cache, positions, block_table, table_stride,
                                         out, out_stride, partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window,
-                                        n_splits, distance, s);
+                                        n_splits, distance, sink, s);
         }
         return launch_for<64, false>(none, 0, nullptr, q, q_stride, cache, positions, block_table, table_stride, out, out_stride,
-                                     partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, s);
+                                     partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, sink, s);
     }
     return launch_for<128, false>(none, 0, nullptr, q, q_stride, cache, positions, block_table, table_stride, out, out_stride,
-                                  partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, s);
+                                  partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, distance, sink, s);
 }

@@ -73,7 +73,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
                          const int32_t* __restrict__ q_start, const int32_t* __restrict__ n_past,
                          const int32_t* __restrict__ block_table, int table_stride, __nv_bfloat16* __restrict__ out,
                          int64_t out_stride, int n_head, int n_kv_head, int page_shift, float scale, int window,
-                         const float* __restrict__ distance) {
+                         const float* __restrict__ distance, const float* __restrict__ sink) {
     constexpr int LD = HD + 8;                  // padded row of a tile in shared memory (elements)
     constexpr int CH = HD / 8;                  // 16-byte chunks per row
     constexpr int KS = HD / 16;                 // k-steps of Q K^T
@@ -245,7 +245,14 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
+    // A head's sink joins each row's divisor once, after all its keys.
+    float f_lo = 1.0f, f_hi = 1.0f;
+    if (sink != nullptr) {
+        const float sk = sink[head] * kLbLog2e;
+        f_lo = lb_sink_join_exp2(sk, m_lo, l_lo);
+        f_hi = lb_sink_join_exp2(sk, m_hi, l_hi);
+    }
+    const float inv_lo = f_lo / l_lo, inv_hi = f_hi / l_hi;
     const size_t out_row = (size_t)(row0 + tile_q * kBM);
 #pragma unroll
     for (int ot = 0; ot < OT; ++ot) {
@@ -262,7 +269,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
 template <int HD>
 int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* q_start, const int32_t* n_past,
            const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len,
-           int n_head, int n_kv_head, int page_shift, float scale, int window, const float* distance, cudaStream_t s) {
+           int n_head, int n_kv_head, int page_shift, float scale, int window, const float* distance, const float* sink, cudaStream_t s) {
     constexpr size_t smem = (size_t)(kBM + 2 * kStages * kBN) * (HD + 8) * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
@@ -272,7 +279,7 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* q_
     dim3 grid((max_q_len + kBM - 1) / kBM, n_head, n_seq);
     LB_CHECK_CUDA(lb_launch_overlapped(prefill_attention_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, q_start, n_past, block_table, table_stride,
-        (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift, scale, window, distance));
+        (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift, scale, window, distance, sink));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
@@ -296,6 +303,14 @@ extern "C" int lb_prefill_attention_biased(const void* q, int64_t q_stride, cons
                                            const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len,
                                            int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance,
                                            void* stream) {
+    return lb_prefill_attention_sink(q, q_stride, cache, q_start, n_past, block_table, table_stride, out, out_stride, n_seq, max_q_len, n_head, n_kv_head,
+                                     head_dim, page_size, scale, window, distance, nullptr, stream);
+}
+
+extern "C" int lb_prefill_attention_sink(const void* q, int64_t q_stride, const void* cache, const int32_t* q_start, const int32_t* n_past,
+                                         const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len,
+                                         int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window, const float* distance,
+                                         const float* sink, void* stream) {
     LB_CHECK_ARG(n_seq >= 0 && max_q_len >= 0, "prefill attention: bad sizes");
     if (!lb_prefill_attention_supports(n_head, n_kv_head, head_dim, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "prefill attention: unsupported shape heads %d/%d head_dim %d page_size %d",
@@ -310,7 +325,7 @@ extern "C" int lb_prefill_attention_biased(const void* q, int64_t q_stride, cons
 #define LB_HD(HD)                                                                                                        \
     case HD:                                                                                                             \
         return launch<HD>(q, q_stride, cache, q_start, n_past, block_table, table_stride, out, out_stride, n_seq, max_q_len, \
-                          n_head, n_kv_head, page_shift, scale, window, distance, s)
+                          n_head, n_kv_head, page_shift, scale, window, distance, sink, s)
     switch (head_dim) {
         LB_HD(16);
         LB_HD(32);

@@ -107,7 +107,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int32_t* __restrict__ q_start, const int32_t* __restrict__ n_past,
                             const int32_t* __restrict__ block_table, int table_stride, __nv_bfloat16* __restrict__ out,
                             int64_t out_stride, int n_head, int n_kv_head, int page_shift, int kv_rows, float scale, int window,
-                            const float* __restrict__ distance, int* status) {
+                            const float* __restrict__ distance, const float* __restrict__ sink, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     lb_wait_for_predecessor();            // queries, keys and values come from the kernel before this one
@@ -390,7 +390,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             float total = c->row_sum[0][r];
 #pragma unroll
             for (int q = 1; q < kParts; ++q) total += c->row_sum[q][r];
-            const float inv = 1.0f / total;
+            // A head's sink joins the row's divisor once, after all its keys (m: the row's maximum in the exponentials' base-2 scale).
+            const float inv = (sink != nullptr ? lb_sink_join_exp2(sink[head] * kLbLog2e, m, total) : 1.0f) / total;
             __nv_bfloat16* dst = out + (size_t)(row0 + tile_q * kBM + r) * out_stride + (size_t)head * kHD + part * 16;
             uint32_t o[16];
             tmem_ld16(t_row + kOCol + part * 16, o);
@@ -436,6 +437,14 @@ extern "C" int lb_prefill_attention_tc_biased(const void* q, int64_t q_stride, i
                                               const int32_t* n_past, const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
                                               int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window,
                                               const float* distance, void* stream) {
+    return lb_prefill_attention_tc_sink(q, q_stride, n_tokens, cache, n_pages, q_start, n_past, block_table, table_stride, out, out_stride, n_seq, max_q_len,
+                                        n_head, n_kv_head, head_dim, page_size, scale, window, distance, nullptr, stream);
+}
+
+extern "C" int lb_prefill_attention_tc_sink(const void* q, int64_t q_stride, int n_tokens, const void* cache, int n_pages, const int32_t* q_start,
+                                            const int32_t* n_past, const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
+                                            int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim, int page_size, float scale, int window,
+                                            const float* distance, const float* sink, void* stream) {
     LB_CHECK_ARG(distance == nullptr || scale != 0.0f, "prefill attention (tcgen05): a penalty by distance needs a factor on the scores that is not zero");
     LB_CHECK_ARG(n_seq >= 0 && max_q_len >= 0 && n_tokens >= 0 && n_pages > 0, "prefill attention: bad sizes");
     if (!lb_prefill_attention_tc_supports(n_head, n_kv_head, head_dim, page_size))
@@ -466,7 +475,7 @@ extern "C" int lb_prefill_attention_tc_biased(const void* q, int64_t q_stride, i
     dim3 grid(n_head * n_seq, (max_q_len + kBM - 1) / kBM);
     LB_CHECK_CUDA(lb_launch_overlapped(prefill_attention_tc_kernel, dim3(grid), dim3(kThreads), smem, static_cast<cudaStream_t>(stream), 
         map_q, map_kv, q_start, n_past, block_table, table_stride, (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift,
-        (int)kv_rows, scale, window, distance, status));
+        (int)kv_rows, scale, window, distance, sink, status));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

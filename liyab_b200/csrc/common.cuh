@@ -114,6 +114,16 @@ __host__ __device__ __forceinline__ int lb_first_visible(int pos, int window) {
 // What a score loses by the distance between query and key, for heads that carry the pair (r1, r2): r1 ln(1 + r2 distance).
 __device__ __forceinline__ float lb_distance_penalty(float r1, float r2, int distance) { return r1 * logf(fmaf(r2, (float)distance, 1.0f)); }
 
+// A head's sink joins a finished softmax state: exp(sink) is added to the divisor, with no key and no value.  `m` is the state's running
+// maximum and `sink` the head's number, both in the scale of the kernel's exponentials (base 2: sink * log2(e)); `l` becomes the new divisor
+// and the result is the factor on the state's weighted values.
+__device__ __forceinline__ float lb_sink_join_exp2(float sink, float m, float& l) {
+    const float top = fmaxf(m, sink), f = exp2f(m - top);
+    l = l * f + exp2f(sink - top);
+    return f;
+}
+constexpr float kLbLog2e = 1.4426950408889634f;
+
 __device__ __forceinline__ float lb_to_float(float v) { return v; }
 __device__ __forceinline__ float lb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

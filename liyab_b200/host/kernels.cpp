@@ -27,8 +27,12 @@ int activation_from_name(const std::string& name) {
 }
 
 namespace {
-// Which of the bfloat16 attention kernels take a sink a head: 1 scalar decode, 2 tensor-core decode, 4 prefill on mma.sync, 8 prefill on tcgen05.
-constexpr int kSinkKernels = 0;
+// Which of the bfloat16 attention kernels run heads with a sink: 1 scalar decode, 2 tensor-core decode, 4 prefill on mma.sync, 8 prefill on
+// tcgen05 (all of them; LIYAB_B200_SINK_KERNELS in the environment, read once, sends such heads to the generic kernel instead, for comparisons).
+const int kSinkKernels = [] {
+    const char* v = std::getenv("LIYAB_B200_SINK_KERNELS");
+    return v != nullptr ? std::atoi(v) : 15;
+}();
 // The latent attention's extras as the kernels take them; `gate`: one float a (token, head), or null.
 lb_latent_extras latent_extras(const LatentShape& a, const Rows* gate, bool with_sink = true, const Rows* latent = nullptr) {
     lb_latent_extras x{};
@@ -270,12 +274,12 @@ void decode_attention(cudaStream_t s, bool tensor_cores, const Rows& q, const vo
     if (n_splits > 1 && (partial == nullptr || counters == nullptr))
         throw invalid_argument("decode attention: scratch buffers are missing");
     if (tensor_cores)
-        check(lb_decode_attention_mma_biased(q.data, q.stride, cache, n_pages, positions, block_table, table_width, out.data, out.stride,
-                                             partial, counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(),
-                                             n_splits, a.distance, s), "decode_attention_mma");
+        check(lb_decode_attention_mma_sink(q.data, q.stride, cache, n_pages, positions, block_table, table_width, out.data, out.stride,
+                                           partial, counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(),
+                                           n_splits, a.distance, a.sink, s), "decode_attention_mma");
     else
-        check(lb_decode_attention_biased(q.data, q.stride, cache, positions, block_table, table_width, out.data, out.stride, partial,
-                                         counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), n_splits, a.distance, s),
+        check(lb_decode_attention_sink(q.data, q.stride, cache, positions, block_table, table_width, out.data, out.stride, partial,
+                                       counters, n_seq, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), n_splits, a.distance, a.sink, s),
               "decode_attention");
 }
 
@@ -290,12 +294,12 @@ void prefill_attention(const Runtime& rt, const Rows& q, int n_tokens, const voi
     const bool tc = prefill_tc_supports(a) && q.stride % 8 == 0 && out.stride % 8 == 0 && aligned16(q.data) &&
                     aligned16(out.data) && blocks <= 4 * static_cast<int64_t>(rt.sm_count) && a.scale > 0;     // it takes the maximum of the raw scores
     if (tc)
-        check(lb_prefill_attention_tc_biased(q.data, q.stride, n_tokens, cache, n_pages, q_start, n_past, block_table, table_width,
-                                             out.data, out.stride, n_seq, max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size,
-                                             a.scale, a.mask(), a.distance, rt.stream), "prefill_attention_tc");
+        check(lb_prefill_attention_tc_sink(q.data, q.stride, n_tokens, cache, n_pages, q_start, n_past, block_table, table_width,
+                                           out.data, out.stride, n_seq, max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size,
+                                           a.scale, a.mask(), a.distance, a.sink, rt.stream), "prefill_attention_tc");
     else
-        check(lb_prefill_attention_biased(q.data, q.stride, cache, q_start, n_past, block_table, table_width, out.data, out.stride, n_seq,
-                                          max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), a.distance, rt.stream),
+        check(lb_prefill_attention_sink(q.data, q.stride, cache, q_start, n_past, block_table, table_width, out.data, out.stride, n_seq,
+                                        max_q_len, a.n_head, a.n_kv_head, a.head_dim, a.page_size, a.scale, a.mask(), a.distance, a.sink, rt.stream),
               "prefill_attention");
 }
 

@@ -200,7 +200,7 @@ CheckpointMap RevudraConfig::checkpoint_map() const {
             m.push_back({p + "feed_forward.up.weight", CheckpointTensor::one(f + "mlp.up", {c.ff, width}, K::Matrix, "none", 0.0, w_std)});
             m.push_back({p + "feed_forward.down.weight", CheckpointTensor::one(f + "mlp.down", {width, c.ff}, K::Matrix, "none", 0.0, inv_sqrt(c.ff))});
         } else if (c.experts > 0) {
-            m.push_back({p + "feed_forward.table", CheckpointTensor::one(f + "mlp.table", {vocab, c.top}, K::Index)});
+            m.push_back({p + "feed_forward.table", CheckpointTensor::one(f + "mlp.table", {vocab, c.top}, K::Index, "none", 0.0, static_cast<double>(c.experts))});
             std::vector<CheckpointSource> gate_up, down;
             for (int64_t e = 0; e < c.experts; ++e) {
                 const std::string ef = std::format("{}mlp.e{}.", f, e);

@@ -359,18 +359,38 @@ void write_random_model(const std::string& model_dir, const ArchitectureConfig& 
         if (!f) throw make_error(Code::Io, "cannot write {}/config.json", model_dir);
         f << raw.dump(1) << "\n";
     }
-    struct Item { std::string name; std::vector<int64_t> shape; double mean, std; std::vector<uint8_t> bytes; };
+    // An index table gets int32 entries below `std` (its upper bound), those of a row all different: row r holds start_r, start_r + 1, ...
+    // (modulo the bound) with start_r drawn from the counter-based generator.
+    struct Item { std::string name; std::vector<int64_t> shape; double mean, std; std::vector<uint8_t> bytes; bool index = false; };
     std::vector<Item> items;
     std::set<std::string> written;          // a file tensor may feed several parameters (slices of one table)
     for (const auto& [dest, spec] : config.checkpoint_map())
         for (const auto& src : spec.sources)
-            if (written.insert(src.name).second) items.push_back({src.name, src.shape, spec.init_mean, spec.init_std, {}});
+            if (written.insert(src.name).second) items.push_back({src.name, src.shape, spec.init_mean, spec.init_std, {}, spec.kind == ParamKind::Index});
     const size_t es = dtype_size(store);
     // Large tensors are cut into pieces so that every core has work.
     struct Piece { size_t item; int64_t first, count; };
     std::vector<Piece> pieces;
     for (size_t i = 0; i < items.size(); ++i) {
         const int64_t n = shape_numel(items[i].shape);
+        if (items[i].index) {
+            Item& it = items[i];
+            const int64_t cols = it.shape.empty() ? 1 : it.shape.back(), rows = n / std::max<int64_t>(cols, 1);
+            const int64_t bound = std::max<int64_t>(static_cast<int64_t>(it.std), 1);
+            if (cols > bound) throw invalid_argument("index table '{}': {} different entries a row do not fit below {}", it.name, cols, bound);
+            it.bytes.resize(static_cast<size_t>(n) * 4);
+            std::vector<double> z(static_cast<size_t>(rows));
+            normal_values(seed, it.name, 0, rows, 0.0, 1.0, z.data());
+            for (int64_t r = 0; r < rows; ++r) {
+                const double u = 0.5 * std::erfc(-z[static_cast<size_t>(r)] / std::sqrt(2.0));
+                const int64_t start = std::min<int64_t>(static_cast<int64_t>(u * static_cast<double>(bound)), bound - 1);
+                for (int64_t j = 0; j < cols; ++j) {
+                    const int32_t e = static_cast<int32_t>((start + j) % bound);
+                    std::memcpy(it.bytes.data() + static_cast<size_t>(r * cols + j) * 4, &e, 4);
+                }
+            }
+            continue;
+        }
         items[i].bytes.resize(static_cast<size_t>(n) * es);
         for (int64_t at = 0; at < n; at += int64_t{1} << 20) pieces.push_back({i, at, std::min<int64_t>(int64_t{1} << 20, n - at)});
     }
@@ -390,7 +410,7 @@ void write_random_model(const std::string& model_dir, const ArchitectureConfig& 
         }
     });
     std::vector<TensorToWrite> out;
-    for (const auto& it : items) out.push_back({it.name, store, it.shape, it.bytes.data()});
+    for (const auto& it : items) out.push_back({it.name, it.index ? DType::I32 : store, it.shape, it.bytes.data()});
     write_safetensors(model_dir + "/model.safetensors", out, Json::object().set("format", "pt").set("seed", std::to_string(seed)));
 }
 

@@ -74,7 +74,7 @@ def window_attention(h, W, p, m, eps, shared, trace=None):
     if m.get("v_mix"):
         if "v_first" in shared:
             lam = W[p + "vmix"]
-            v = (1.0 - lam) * v + lam * shared["v_first"]
+            v = (1.0 - lam) * v + lam * shared["v_first"].reshape(v.shape)      # a token's values side by side, however the heads cut them
         else:
             shared["v_first"] = v
     size = m["mask"]["size"]
@@ -85,9 +85,9 @@ def window_attention(h, W, p, m, eps, shared, trace=None):
             lo = max(0, i - size + 1)
             s = (k[lo:i + 1, g] @ q[i, a]) * m["scale"]
             out[i, a] = softmax_with_sink(s, W[p + "sink"][a]) @ v[lo:i + 1, g]
-    if trace is not None:
-        trace.update(q=q, k=k, v=v, attention=out.reshape(n, H * E))
     gated = out.reshape(n, H * E) * sigmoid(h @ W[p + "g"].T)
+    if trace is not None:
+        trace.update(q=q, k=k, v=v, attention=out.reshape(n, H * E), gated=gated)
     return gated @ W[p + "o"].T
 
 
@@ -130,10 +130,11 @@ def latent_attention(h, W, p, m, eps, trace=None):
         for i in range(n):
             s = (k_plain[:i + 1, a] @ q_plain[i, a] + shared_key[:i + 1] @ q_rot[i, a]) * m["scale"]
             out[i, a] = softmax_with_sink(s, W[p + "sink"][a]) @ v[:i + 1, a]
-    if trace is not None:
-        trace.update(latent=c, shared_key=shared_key, attention=out.reshape(n, H * E))
     gate = sigmoid(h @ W[p + "g"].T)                     # one number a head
-    return (out * gate[:, :, None]).reshape(n, H * E) @ W[p + "o"].T
+    gated = (out * gate[:, :, None]).reshape(n, H * E)
+    if trace is not None:
+        trace.update(latent=c, shared_key=shared_key, attention=out.reshape(n, H * E), gated=gated)
+    return gated @ W[p + "o"].T
 
 
 # ---- feed-forwards -------------------------------------------------------------------------------------------
