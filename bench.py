@@ -6,6 +6,7 @@
     python bench.py --design puzutar [--size small]   # Puzutar at GPT-2's layer sizes beside GPT-2 itself (see puzutar_line)
     python bench.py --design vosurax [--size small]   # Vosurax likewise (see vosurax_line)
     python bench.py --design viresun [--size small]   # Viresun beside Vosurax and GPT-2 (see viresun_line)
+    python bench.py --design revudra [--size small]   # Revudra beside Vosurax and GPT-2 (see revudra_line)
 
 A step is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (12 layers, width 768, 12 heads) with random weights, a batch of
@@ -506,6 +507,101 @@ def viresun_line(args) -> int:
     return 0
 
 
+def revudra_config(size, layers=0):
+    """Revudra with the width, depth, head count, inner width and vocabulary of a GPT-2 size.  Of every four blocks the first is attention
+    under a window of 512 (heads of 64, a quarter as many key/value heads, half of a head rotated, values blended from the second such
+    block on) with the dense feed-forward; the second and third are matrix memories (heads of 64 x 64, decays from 0.94 to 0.998) and the
+    fourth attention over latent rows (heads of 48 + 16 rotated values, a latent of 256, queries through a latent of half the width);
+    these three have 16 experts of a quarter of the inner width, two a token by the table."""
+    g = SIZES[size]
+    L, W, H = max(4, layers or g["n_layer"]), g["n_embd"], g["n_head"]
+    attn = dict(heads=H, kv_heads=max(1, H // 4), dim=64, vdim=64, scale=0.125, mask=dict(size=512), rot=dict(base=1e6, dims=32), v_mix=True)
+    memory = dict(heads=H, dim=64, vdim=64, decay=[1.0 - 2.0 ** (-4 - 5 * h / H) for h in range(H)])
+    latent = dict(heads=H, dim=48, rot_dim=16, vdim=64, kv_rank=256, q_rank=W // 2, scale=0.125, rot=dict(base=1e4, dims=16))
+    dense = dict(kind="dense", ff=g["n_inner"])
+    moe = dict(kind="moe", expert=dict(ff=g["n_inner"] // 4), router=dict(experts=16, top=2))
+    kinds = [("attention", attn, dense), ("lightning", memory, moe), ("lightning", memory, moe), ("latent_attention", latent, moe)]
+    blocks = [dict(type=kinds[i % 4][0], mixer=kinds[i % 4][1], mlp=kinds[i % 4][2]) for i in range(L)]
+    return dict(architecture="Revudra", vocab=g["vocab_size"], width=W, norm=dict(eps=1e-5), residual_mult=0.7, embedding=dict(scale=1.0), logit_scale=1.0,
+                max_positions=g["n_positions"], layers=blocks)
+
+
+def revudra_bytes_and_flops(cfg, dtype_bytes, batch):
+    """Bytes a decode step of `batch` requests must read (weights its rows touch, memories read and written, visible cache rows) and the
+    FLOPs of a prefill (products with the weights a token uses, attention inside its window or over the latent rows as it is computed, the
+    memories' updates and reads)."""
+    W, V = cfg["width"], cfg["vocab"]
+    step_bytes, token_flops, attn, lat, mem = 2 * V * W * dtype_bytes, 2 * V * W, [], [], []
+    for l in cfg["layers"]:
+        m, mlp = l["mixer"], l["mlp"]
+        H = m["heads"]
+        if l["type"] == "attention":
+            mats = W * (H * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"]) + H * m["vdim"]) + W * H * m["vdim"]
+            attn.append((H, m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]))
+        elif l["type"] == "lightning":
+            mats = W * H * (2 * m["dim"] + 2 * m["vdim"]) + W * H * m["vdim"]
+            mem.append((H, m["dim"], m["vdim"]))
+        else:
+            row = m["kv_rank"] + m["rot_dim"]
+            mats = W * (m["q_rank"] + row + H) + m["q_rank"] * H * (m["dim"] + m["rot_dim"]) + H * m["kv_rank"] * (m["dim"] + m["vdim"]) + W * H * m["vdim"]
+            lat.append((H, m["kv_rank"], m["rot_dim"]))
+        used = touched = mats
+        if mlp and mlp["kind"] == "dense":
+            used += 2 * W * mlp["ff"]
+            touched += 2 * W * mlp["ff"]
+        elif mlp:
+            E, top, F = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+            used += 3 * W * top * F
+            touched += 3 * W * F * E * (1.0 - (1.0 - top / E) ** batch)      # the experts a batch is expected to touch
+        token_flops += 2 * used
+        step_bytes += touched * dtype_bytes
+    state_bytes = sum(2 * 4 * H * (D * E + D + 1) for H, D, E in mem)
+    cache_row_bytes = [dtype_bytes * 2 * G * max(D, E) for _, G, D, E, _ in attn]
+    latent_row_bytes = [dtype_bytes * (C + R) for _, C, R in lat]
+
+    def decode_bytes(mean_context):
+        return step_bytes + batch * (state_bytes + sum(b * min(mean_context, c) for b, (_, _, _, _, c) in zip(cache_row_bytes, attn)) +
+                                     sum(b * mean_context for b in latent_row_bytes))
+
+    def prefill_flops(seq_lens, rows):
+        total = sum(seq_lens) * (token_flops - 2 * V * W) + 2 * rows * V * W
+        for H, G, D, E, c in attn:
+            total += sum(2 * H * (D + E) * sum(min(i + 1, c) for i in range(s)) for s in seq_lens)
+        for H, C, R in lat:
+            total += sum(2 * H * (2 * C + R) * s * (s + 1) // 2 for s in seq_lens)
+        for H, D, E in mem:
+            total += sum(seq_lens) * 4 * H * D * E
+        return total
+
+    return decode_bytes, prefill_flops
+
+
+def revudra_line(args) -> int:
+    """--design revudra: decode (batch 1 / 8 / 64, 512-token prompts) and prefill (2 x 1024 tokens) of Revudra at the layer sizes of
+    GPT-2 `--size`, and the same four figures of Vosurax (the engine's closest design: attention with normed queries and keys under a
+    mask and a gate, a matrix memory per head with a fixed decay, small gated experts) and of GPT-2 at that size."""
+    from liyab_b200.weights import write_random_model
+    pk = peaks()
+    dtype_bytes = 2 if args.dtype == "bfloat16" else 4
+    cfg = revudra_config(args.size, args.layers)
+    steps = min(args.steps, 128)
+    out = {"design": "revudra", "size": args.size, "dtype": args.dtype, "peaks": pk["source"],
+           "config": {k: cfg[k] for k in ("width", "vocab", "norm")} | {"layers": len(cfg["layers"]), "attention": cfg["layers"][0]["mixer"],
+                                                                         "memory": {k: v for k, v in cfg["layers"][1]["mixer"].items() if k != "decay"},
+                                                                         "latent_attention": cfg["layers"][3]["mixer"], "experts": cfg["layers"][1]["mlp"]}}
+    with tempfile.TemporaryDirectory(prefix="liyab_b200_bench_") as tmp:
+        folder = write_random_model(os.path.join(tmp, "revudra"), cfg, seed=0, dtype=args.dtype)
+        out["revudra"] = design_block(folder, args.dtype, steps, pk, lambda b: revudra_bytes_and_flops(cfg, dtype_bytes, b))
+        other = vosurax_config(args.size, args.layers + 2 if args.layers else 0)
+        folder = write_random_model(os.path.join(tmp, "vosurax"), other, seed=0, dtype=args.dtype)
+        out["vosurax"] = design_block(folder, args.dtype, steps, pk, lambda b: vosurax_bytes_and_flops(other, dtype_bytes, b))
+        if not args.layers:
+            out["gpt2"], _ = size_block(tmp, args.size, args.dtype, steps, pk)
+    print(json.dumps(out))
+    return 0
+
+
+
 def reference_arm(args) -> int:
     from baseline.reference_arm import run
     return run(args)
@@ -523,8 +619,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="the headline figure only")
     ap.add_argument("--no-extra", action="store_true", help="skip the 32-bit engine, the other sizes and the mixed workload")
-    ap.add_argument("--design", default="gpt2", choices=["gpt2", "puzutar", "vosurax", "viresun"],
-                    help="puzutar, vosurax, viresun: that design at the layer sizes of GPT-2 --size beside GPT-2 itself (its own JSON line; the default run is unchanged)")
+    ap.add_argument("--design", default="gpt2", choices=["gpt2", "puzutar", "vosurax", "viresun", "revudra"],
+                    help="puzutar, vosurax, viresun, revudra: that design at the layer sizes of GPT-2 --size beside GPT-2 itself (its own JSON line; the default run is unchanged)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -534,6 +630,8 @@ def main() -> int:
         return vosurax_line(args)
     if args.design == "viresun":
         return viresun_line(args)
+    if args.design == "revudra":
+        return revudra_line(args)
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (run with --gpus 1)")
         return 2

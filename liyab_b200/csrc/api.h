@@ -477,6 +477,14 @@ int lb_latent_attention_mma_ext(const void* wide, int64_t ldw, const void* cache
                                 int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window, int n_splits,
                                 int merge_parts, const lb_latent_extras* extras, void* stream);
 
+/* lb_rms_sum_add that also leaves the new rows of x rounded to bfloat16 in x16 (rows ld16 apart; null: as lb_rms_sum_add), for the part that
+ * reads the stream next. */
+int lb_rms_sum_add_rounded(float* x, int64_t ldx, int n_branches, const float* const* y, const int64_t* ldy, const float* const* weight, int n_rows,
+                           int width, float scale, float eps, void* x16, int64_t ld16, void* stream);
+/* lb_expert_combine_weighted that, with `overwrite`, writes the rows' sums to x instead of adding them. */
+int lb_expert_combine_into(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, const float* weights, int n_rows, int width, int top,
+                           int overwrite, void* stream);
+
 /* Queries, keys and values of a float projection on their way to attention (see rotary_rows.cu).  norm_mode 0 none, 1 every head over its
  * root mean square (gains [dim]), 2 all of q and all of k each over one root mean square (gains [n_head * dim], [n_kv_head * dim]); then the
  * first rot_dims values of every query and key head rotated (value i with i + rot_dims / 2, angle positions[t] * freq[i]).  Values: with

@@ -32,7 +32,8 @@ struct Branches {
     int n;
 };
 
-__global__ void rms_sum_add_kernel(float* __restrict__ x, int64_t ldx, Branches b, int width, float scale, float eps) {
+__global__ void rms_sum_add_kernel(float* __restrict__ x, int64_t ldx, Branches b, int width, float scale, float eps, __nv_bfloat16* __restrict__ x16,
+                                   int64_t ld16) {
     __shared__ float scratch[33];
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
@@ -75,7 +76,9 @@ __global__ void rms_sum_add_kernel(float* __restrict__ x, int64_t ldx, Branches 
                 if (b.w[i] != nullptr) v *= b.w[i][c];
                 acc += v;
             }
-            x[(size_t)r * ldx + c] += scale * acc;
+            const float sum = x[(size_t)r * ldx + c] + scale * acc;
+            x[(size_t)r * ldx + c] = sum;
+            if (x16 != nullptr) x16[(size_t)r * ld16 + c] = __float2bfloat16_rn(sum);
         }
         return;
     }
@@ -86,7 +89,9 @@ __global__ void rms_sum_add_kernel(float* __restrict__ x, int64_t ldx, Branches 
             if (b.w[i] != nullptr) v *= b.w[i][c];
             acc += v;
         }
-        x[(size_t)r * ldx + c] += scale * acc;
+        const float sum = x[(size_t)r * ldx + c] + scale * acc;
+        x[(size_t)r * ldx + c] = sum;
+        if (x16 != nullptr) x16[(size_t)r * ld16 + c] = __float2bfloat16_rn(sum);
     }
 }
 
@@ -209,6 +214,11 @@ extern "C" int lb_add_row(float* x, int64_t ldx, const float* v, int n_rows, int
 
 extern "C" int lb_rms_sum_add(float* x, int64_t ldx, int n_branches, const float* const* y, const int64_t* ldy, const float* const* weight, int n_rows,
                               int width, float scale, float eps, void* stream) {
+    return lb_rms_sum_add_rounded(x, ldx, n_branches, y, ldy, weight, n_rows, width, scale, eps, nullptr, 0, stream);
+}
+
+extern "C" int lb_rms_sum_add_rounded(float* x, int64_t ldx, int n_branches, const float* const* y, const int64_t* ldy, const float* const* weight,
+                                      int n_rows, int width, float scale, float eps, void* x16, int64_t ld16, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && width > 0 && n_branches >= 1 && n_branches <= 4, "rms_sum_add: %d branches (1 to 4)", n_branches);
     if (n_rows == 0) return LB_OK;
     Branches b{};
@@ -219,7 +229,8 @@ extern "C" int lb_rms_sum_add(float* x, int64_t ldx, int n_branches, const float
         b.w[i] = weight != nullptr ? weight[i] : nullptr;
     }
     const int threads = width > 512 ? 256 : 128;
-    LB_CHECK_CUDA(lb_launch_overlapped(rms_sum_add_kernel, dim3(n_rows), dim3(threads), 0, static_cast<cudaStream_t>(stream), x, ldx, b, width, scale, eps));
+    LB_CHECK_CUDA(lb_launch_overlapped(rms_sum_add_kernel, dim3(n_rows), dim3(threads), 0, static_cast<cudaStream_t>(stream), x, ldx, b, width, scale, eps,
+                                       static_cast<__nv_bfloat16*>(x16), ld16));
     return LB_OK;
 }
 

@@ -499,7 +499,7 @@ int launch_product_rows(const ProductArgs& p, int n_pairs, cudaStream_t s) {
 }
 
 __global__ void expert_combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ place,
-                                      int n_rows, int width, int top, const float* __restrict__ weights) {
+                                      int n_rows, int width, int top, const float* __restrict__ weights, int overwrite) {
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const long total = (long)n_rows * width;
@@ -511,7 +511,8 @@ __global__ void expert_combine_kernel(float* __restrict__ x, int64_t ldx, const 
             for (int k = 0; k < top; ++k) acc = fmaf(weights[t * top + k], y[(size_t)place[t * top + k] * ldy + c], acc);
         else
             for (int k = 0; k < top; ++k) acc += y[(size_t)place[t * top + k] * ldy + c];
-        x[(size_t)t * ldx + c] += acc;
+        if (overwrite) x[(size_t)t * ldx + c] = acc;
+        else x[(size_t)t * ldx + c] += acc;
     }
 }
 
@@ -596,11 +597,16 @@ extern "C" int lb_expert_combine(float* x, int64_t ldx, const float* y, int64_t 
 
 extern "C" int lb_expert_combine_weighted(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, const float* weights, int n_rows,
                                           int width, int top, void* stream) {
+    return lb_expert_combine_into(x, ldx, y, ldy, place, weights, n_rows, width, top, 0, stream);
+}
+
+extern "C" int lb_expert_combine_into(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, const float* weights, int n_rows,
+                                      int width, int top, int overwrite, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && width > 0 && top > 0, "expert combine: bad sizes");
     if (n_rows == 0) return LB_OK;
     const long total = (long)n_rows * width;
     const int blocks = (int)min((total + 255) / 256, (long)148 * 16);
     LB_CHECK_CUDA(lb_launch_overlapped(expert_combine_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), x, ldx, y, ldy, place, n_rows, width,
-                                       top, weights));
+                                       top, weights, overwrite));
     return LB_OK;
 }

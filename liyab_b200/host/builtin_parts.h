@@ -399,15 +399,15 @@ public:
         const int T = ctx.n_tokens;
         const Rows y = ctx.workspace->get("block.sublayer", T, x.cols, DType::F32);
         ctx.phase(Phase::Mixer);
-        mixer.forward_into(ctx, input(ctx, x), y, unit);
+        mixer.forward_into(ctx, input(ctx, x, unit.entry - 1), y, unit);
         ctx.tap("mixer.out", y);
-        join(ctx, mixer_norm, y, x);
+        join(ctx, mixer_norm, y, x, unit.entry);
         ctx.tap("mixer", x);
         if (feed_forward == nullptr) return;
         ctx.phase(Phase::FeedForward);
-        feed_forward->forward_into(ctx, input(ctx, x), y);
+        feed_forward->forward_into(ctx, input(ctx, x, unit.entry), y);
         ctx.tap("feed_forward.out", y);
-        join(ctx, *ff_norm, y, x);
+        join(ctx, *ff_norm, y, x, unit.entry);
         ctx.tap("feed_forward", x);
     }
     Mixer& mixer;
@@ -422,16 +422,25 @@ private:
         if (!r || !r->rms || r->offset != nullptr || r->gain_offset != 0.0f)
             throw unsupported("arrangement 'sublayer_norm' takes RMS norms over the whole row (gain only) on its sublayers' outputs");
     }
-    // What a sublayer reads: the stream itself in float32, its rows rounded to the compute type otherwise.
-    Rows input(StepContext& ctx, const Rows& x) const {
+    // What a sublayer reads: the stream itself in float32, its rows rounded to the compute type otherwise.  The sum before (this block's,
+    // or that of the run numbered `left_by`) has left the rounded rows already; only a block that finds none rounds them itself.
+    Rows input(StepContext& ctx, const Rows& x, int left_by) const {
         if (ctx.runtime.dtype == DType::F32) return x;
         const Rows h = ctx.workspace->get("block.input", ctx.n_tokens, x.cols, ctx.runtime.dtype);
+        if (ctx.stream_rounded_entry >= 0 && ctx.stream_rounded_entry == left_by && ctx.stream_rounded.data == h.data) return h;
         kernels::rows_to_bf16(ctx.stream(), x, h, ctx.n_tokens);
         return h;
     }
-    void join(StepContext& ctx, const Norm& n, const Rows& y, const Rows& x) const {
+    void join(StepContext& ctx, const Norm& n, const Rows& y, const Rows& x, int entry) const {
         const NormRecipe r = *n.recipe();
-        kernels::rms_sum_add(ctx.stream(), x, {y}, {r.gain}, ctx.n_tokens, scale, r.eps);
+        if (ctx.runtime.dtype == DType::F32) {
+            kernels::rms_sum_add(ctx.stream(), x, {y}, {r.gain}, ctx.n_tokens, scale, r.eps);
+            return;
+        }
+        const Rows h = ctx.workspace->get("block.input", ctx.n_tokens, x.cols, ctx.runtime.dtype);
+        kernels::rms_sum_add(ctx.stream(), x, {y}, {r.gain}, ctx.n_tokens, scale, r.eps, &h);
+        ctx.stream_rounded = h;
+        ctx.stream_rounded_entry = entry;
     }
     LayerParts keep_;
 };

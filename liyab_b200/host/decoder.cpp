@@ -155,6 +155,7 @@ Rows DecoderModel::forward(StepContext& ctx) {
     Workspace& ws = *ctx.workspace;
     const Rows x = ws.get("residual", T, width, DType::F32);
     ctx.phase(Phase::Embed);
+    ctx.stream_rounded_entry = -1;
     position->embed(ctx, embedding, static_cast<float>(spec.embedding.scale), x);
     ctx.tap("embed", x);
     for (size_t i = 0; i < spec.run_order.size(); ++i) {
@@ -162,6 +163,7 @@ Rows DecoderModel::forward(StepContext& ctx) {
         if (e.offset_row >= 0) {
             kernels::add_row(ctx.stream(), x, pass_offsets + static_cast<int64_t>(e.offset_row) * width, T);
             ctx.tap("pass_offset", x);
+            ctx.stream_rounded_entry = -1;
         }
         layers[static_cast<size_t>(e.layer)].block->forward(ctx, x, CacheUnit{e.cache, e.cache == static_cast<int>(i), static_cast<int>(i)});
     }

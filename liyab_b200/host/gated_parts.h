@@ -546,7 +546,10 @@ public:
         return out;
     }
     bool capturable() const override { return true; }
-    void forward(StepContext& ctx, const Rows& h, const Rows& x) override {
+    void forward(StepContext& ctx, const Rows& h, const Rows& x) override { run(ctx, h, x, false); }
+    // The rows' sums are written instead of added, so nothing has to be cleared first (a shared expert then adds to them).
+    void forward_into(StepContext& ctx, const Rows& h, const Rows& y) override { run(ctx, h, y, true); }
+    void run(StepContext& ctx, const Rows& h, const Rows& x, bool overwrite) {
         const int T = ctx.n_tokens, pairs = T * top;
         Workspace& ws = *ctx.workspace;
         cudaStream_t s = ctx.stream();
@@ -566,7 +569,7 @@ public:
         kernels::expert_product(s, true, h, gate_up, experts, offsets, pair_at, weight_on_output ? nullptr : weights, mid, pairs, static_cast<int>(inner),
                                 static_cast<int>(hidden), top, gate, alpha, limit);
         kernels::expert_product(s, false, mid, down, experts, offsets, pair_at, weights, y, pairs, static_cast<int>(hidden), static_cast<int>(inner), top, gate);
-        kernels::expert_combine(s, x, y, place, T, top, weight_on_output ? weights : nullptr);
+        kernels::expert_combine(s, x, y, place, T, top, weight_on_output ? weights : nullptr, overwrite);
         ctx.tap("routed", x);
         if (shared) shared->forward(ctx, h, x);
     }

@@ -314,7 +314,9 @@ void add_row(cudaStream_t s, const Rows& x, const float* v, int n_rows) {
     check(lb_add_row(x.f32(), x.stride, v, n_rows, static_cast<int>(x.cols), s), "add_row");
 }
 
-void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, const std::vector<const float*>& weight, int n_rows, float scale, float eps) {
+void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, const std::vector<const float*>& weight, int n_rows, float scale, float eps,
+                 const Rows* rounded) {
+    if (rounded != nullptr && (rounded->dtype != DType::BF16 || rounded->cols != x.cols)) throw invalid_argument("rms_sum_add: the rounded rows are bfloat16 of the stream's width");
     if (y.empty() || y.size() > 4 || weight.size() != y.size() || x.dtype != DType::F32) throw invalid_argument("rms_sum_add: one to four float branches with a weight each");
     const float* ys[4];
     int64_t ld[4];
@@ -323,7 +325,8 @@ void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, cons
         ys[i] = y[i].f32();
         ld[i] = y[i].stride;
     }
-    check(lb_rms_sum_add(x.f32(), x.stride, static_cast<int>(y.size()), ys, ld, weight.data(), n_rows, static_cast<int>(x.cols), scale, eps, s), "rms_sum_add");
+    check(lb_rms_sum_add_rounded(x.f32(), x.stride, static_cast<int>(y.size()), ys, ld, weight.data(), n_rows, static_cast<int>(x.cols), scale, eps,
+                                 rounded != nullptr ? rounded->data : nullptr, rounded != nullptr ? rounded->stride : 0, s), "rms_sum_add");
 }
 
 void qk_norm_store(cudaStream_t s, const Rows& proj, const QkvColumns& c, const float* q_weight, const float* k_weight, const Rows& q_out, void* cache,
@@ -446,9 +449,9 @@ void expert_product(cudaStream_t s, bool gated, const Rows& a, const Tensor& w, 
                                  weights, out.data, out.stride, n_pairs, n_experts, n, k, top, gate, alpha, limit, s), "expert_product");
 }
 
-void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top, const float* weights) {
+void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top, const float* weights, bool overwrite) {
     if (x.dtype != DType::F32 || y.dtype != DType::F32 || x.cols != y.cols) throw invalid_argument("expert combine: buffers do not fit");
-    check(lb_expert_combine_weighted(x.f32(), x.stride, y.f32(), y.stride, place, weights, n_rows, static_cast<int>(x.cols), top, s), "expert_combine");
+    check(lb_expert_combine_into(x.f32(), x.stride, y.f32(), y.stride, place, weights, n_rows, static_cast<int>(x.cols), top, overwrite ? 1 : 0, s), "expert_combine");
 }
 
 void ssm_prepare(cudaStream_t s, const Rows& proj, const float* taps, const float* tap_bias, const float* dt_bias, const float* a_log, float* conv_state,

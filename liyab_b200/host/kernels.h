@@ -176,7 +176,9 @@ void latent_attention(cudaStream_t s, DType cache_dtype, const Rows& wide, const
 // x[r, :] += v (float [width]) for the first n_rows rows.
 void add_row(cudaStream_t s, const Rows& x, const float* v, int n_rows);
 // x[r, :] += scale * sum_i rms(y_i[r, :]) * weight_i over up to four branches (float rows; a weight may be null).
-void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, const std::vector<const float*>& weight, int n_rows, float scale, float eps);
+// With `rounded` (bfloat16 rows) the new rows of x are also left there, rounded once, for the part that reads the stream next.
+void rms_sum_add(cudaStream_t s, const Rows& x, const std::vector<Rows>& y, const std::vector<const float*>& weight, int n_rows, float scale, float eps,
+                 const Rows* rounded = nullptr);
 // Queries, keys and values of a float projection on their way to attention: per-head RMS norm of queries and keys (gains may be null),
 // queries into q_out [T, n_head * padded], keys and values into the cache pages (heads padded with zeros to `padded` values).
 struct QkvColumns {
@@ -240,7 +242,8 @@ void expert_plan(cudaStream_t s, const int32_t* ids, int n_pairs, int n_experts,
 void expert_product(cudaStream_t s, bool gated, const Rows& a, const Tensor& w, int n_experts, const int32_t* offsets, const int32_t* pair_at,
                     const float* weights, const Rows& out, int n_pairs, int n, int k, int top, int gate, float alpha = 0.0f, float limit = 0.0f);
 // With `weights` [rows, top] every result is multiplied by its weight as it is added.
-void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top, const float* weights = nullptr);
+// `overwrite`: the sums are written to x instead of added.
+void expert_combine(cudaStream_t s, const Rows& x, const Rows& y, const int32_t* place, int n_rows, int top, const float* weights = nullptr, bool overwrite = false);
 
 // ---- the pieces around a state space per head whose step depends on the input (the recurrence is the matrix memory's) ----
 struct StateSpaceShape {

@@ -113,6 +113,11 @@ struct StepContext {
     int max_positions = 0;          // the longest sequence the engine serves (fixes split counts and table widths)
     const TapFn* tap_fn = nullptr;  // when set, parts' outputs are shown to it (tests)
     PhaseTimer* phases = nullptr;   // when set, phase boundaries are recorded
+    // The residual stream rounded to the compute type, where the run numbered `stream_rounded_entry` left it beside its last sum into the
+    // stream (-1: nobody did); the next run may read it instead of rounding the stream again.  The model clears it whenever something
+    // else changes the stream.
+    Rows stream_rounded;
+    int stream_rounded_entry = -1;
 
     cudaStream_t stream() const { return runtime.stream; }
     // The unit's pages [page, K|V, kv_head, slot, head_dim] and its group's view.

@@ -17,7 +17,7 @@ from .csrc.build import load_library
 from .status import ErrorCode, LiyabError, invalid_argument
 
 F32, BF16 = 0, 1
-ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2, "xielu": 3}      # xielu: the bias holds N + 2 values, the last two the learned pair
+ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2, "xielu": 3, "relu2": 4}      # xielu: the bias holds N + 2 values, the last two the learned pair
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 _c = ctypes
@@ -54,6 +54,15 @@ _SIGNATURES = {
     "lb_decode_attention_mma_biased": [_p, _l, _p, _i, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p],
     "lb_prefill_attention_biased": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
     "lb_prefill_attention_tc_biased": [_p, _l, _i, _p, _i, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
+    "lb_paged_attention_generic_sink": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p],
+    "lb_decode_attention_sink": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p, _p],
+    "lb_decode_attention_mma_sink": [_p, _l, _p, _i, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p, _p],
+    "lb_prefill_attention_sink": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p],
+    "lb_prefill_attention_tc_sink": [_p, _l, _i, _p, _i, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p, _p],
+    "lb_qkv_rotary_store": [_i, _p, _l, _i, _i, _i, _p, _p, _p, _l, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _p, _i, _p, _p, _l, _p, _p],
+    "lb_row_norm_gate": [_i, _p, _l, _p, _l, _p, _p, _l, _i, _i, _i, _f, _p],
+    "lb_activate_columns": [_p, _l, _i, _i, _i, _p],
+    "lb_router_table": [_p, _p, _p, _p, _i, _i, _i, _i, _p],
 }
 
 _lib = None
@@ -345,18 +354,20 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
 
 def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, tok_seq: torch.Tensor, positions: torch.Tensor,
                             block_table: torch.Tensor, out: torch.Tensor, n_tokens: int, n_head: int, n_kv_head: int,
-                            head_dim: int, page_size: int, scale: float, window: int = 0, distance: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            head_dim: int, page_size: int, scale: float, window: int = 0, distance: Optional[torch.Tensor] = None,
+                            sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the step's tokens over their requests' pages, 32-bit arithmetic.  `distance` (float32, r1 [n_head] then
-    r2 [n_head]): the score of the key d positions back loses r1 ln(1 + r2 d)."""
+    r2 [n_head]): the score of the key d positions back loses r1 ln(1 + r2 d).  `sink` (float32 [n_head]): exp(sink[h]) joins the divisor
+    of head h's softmax, with no key and no value."""
     if q.dtype != cache.dtype or out.dtype != cache.dtype:
         raise invalid_argument("attention: q, cache and out must have one element type")
     if q.stride(1) != 1 or out.stride(1) != 1:
         raise invalid_argument("attention: q and out must be dense within a row")
-    check(lib().lb_paged_attention_generic_biased(
+    check(lib().lb_paged_attention_generic_sink(
         _code(cache.dtype, "cache"), _dev(q, "q"), q.stride(0), _dev(cache, "cache"),
         _dev(tok_seq, "tok_seq", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
-        n_tokens, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), _distance(distance, n_head), stream_ptr()),
+        n_tokens, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), _distance(distance, n_head), _sink(sink, n_head), stream_ptr()),
         "paged_attention_generic")
     return out
 
@@ -365,6 +376,12 @@ def _distance(distance: Optional[torch.Tensor], n_head: int) -> Optional[int]:
     if distance is not None and (distance.numel() != 2 * n_head or not distance.is_contiguous()):
         raise invalid_argument("attention: the penalty by distance is r1 [n_head] then r2 [n_head]")
     return _opt(distance, "distance", torch.float32)
+
+
+def _sink(sink: Optional[torch.Tensor], n_head: int) -> Optional[int]:
+    if sink is not None and (sink.numel() != n_head or not sink.is_contiguous()):
+        raise invalid_argument("attention: the sinks are one float a head")
+    return _opt(sink, "sink", torch.float32)
 
 
 def decode_attention_kernels(n_head: int, n_kv_head: int, head_dim: int, page_size: int) -> tuple:
@@ -394,7 +411,8 @@ def decode_splits(n_seq: int, n_kv_head: int, max_context: int = 0, tensor_cores
 def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                      out: torch.Tensor, partial: Optional[torch.Tensor], counters: Optional[torch.Tensor], n_seq: int,
                      n_head: int, n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int,
-                     n_splits: int, tensor_cores: Optional[bool] = None, distance: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     n_splits: int, tensor_cores: Optional[bool] = None, distance: Optional[torch.Tensor] = None,
+                     sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one new token per request over its pages (bfloat16), keys split `n_splits` ways.
     `tensor_cores`: None picks the tensor-core kernel where it takes the shape, else the scalar one.  `distance`: as for
     paged_attention_generic."""
@@ -409,12 +427,12 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tens
     if tensor_cores is None:
         tensor_cores = decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)[1]
     cache_args = (_dev(cache, "cache"), cache.shape[0]) if tensor_cores else (_dev(cache, "cache"),)
-    fn = lib().lb_decode_attention_mma_biased if tensor_cores else lib().lb_decode_attention_biased
+    fn = lib().lb_decode_attention_mma_sink if tensor_cores else lib().lb_decode_attention_sink
     check(fn(
         _dev(q, "q"), q.stride(0), *cache_args, _dev(positions, "positions", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
         _opt(partial, "partial", torch.float32), _opt(counters, "counters", torch.int32), n_seq, n_head, n_kv_head,
-        head_dim, page_size, float(scale), int(window), int(n_splits), _distance(distance, n_head), stream_ptr()), "decode_attention")
+        head_dim, page_size, float(scale), int(window), int(n_splits), _distance(distance, n_head), _sink(sink, n_head), stream_ptr()), "decode_attention")
     return out
 
 
@@ -439,7 +457,7 @@ def prefill_attention_tc_supports(n_head: int, n_kv_head: int, head_dim: int, pa
 def prefill_attention(q: torch.Tensor, cache: torch.Tensor, q_start: torch.Tensor, n_past: torch.Tensor,
                       block_table: torch.Tensor, out: torch.Tensor, n_seq: int, max_q_len: int, n_head: int,
                       n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int = 0,
-                      tcgen05: Optional[bool] = None, distance: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      tcgen05: Optional[bool] = None, distance: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the step's prompt portions over their pages (bfloat16, tensor cores).  `tcgen05`: None picks
     the tcgen05 kernel where it takes the shape and the rows are 16-byte aligned, else the mma.sync one.  `distance`: as for
     paged_attention_generic."""
@@ -456,18 +474,18 @@ def prefill_attention(q: torch.Tensor, cache: torch.Tensor, q_start: torch.Tenso
                    and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
                    and blocks <= 4 * _sm_count(q.device))
     if tcgen05:
-        check(lib().lb_prefill_attention_tc_biased(
+        check(lib().lb_prefill_attention_tc_sink(
             _dev(q, "q"), q.stride(0), q.shape[0], _dev(cache, "cache"), cache.shape[0],
             _dev(q_start, "q_start", torch.int32), _dev(n_past, "n_past", torch.int32),
             _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0), n_seq,
-            max_q_len, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), _distance(distance, n_head), stream_ptr()),
+            max_q_len, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), _distance(distance, n_head), _sink(sink, n_head), stream_ptr()),
             "prefill_attention_tc")
         return out
-    check(lib().lb_prefill_attention_biased(
+    check(lib().lb_prefill_attention_sink(
         _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(q_start, "q_start", torch.int32),
         _dev(n_past, "n_past", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.stride(0),
         _dev(out, "out"), out.stride(0), n_seq, max_q_len, n_head, n_kv_head, head_dim, page_size, float(scale),
-        int(window), _distance(distance, n_head), stream_ptr()), "prefill_attention")
+        int(window), _distance(distance, n_head), _sink(sink, n_head), stream_ptr()), "prefill_attention")
     return out
 
 
@@ -825,3 +843,46 @@ def ssm_prepare(proj: torch.Tensor, xbc_off: int, dt_off: int, taps: torch.Tenso
                                _dev(q_start, "q_start", torch.int32), _dev(slots, "slots", torch.int32), _dev(out, "out", torch.float32), out.stride(0),
                                proj.shape[0], q_start.numel() - 1, n_head, vdim, group_values, taps.shape[1], int(decode_only), stream_ptr()), "ssm_prepare")
     return out
+
+
+# ------------------------------------------------------------------ rows around rotated attention, norms over all heads, experts by table
+
+def qkv_rotary_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                     q_out: torch.Tensor, cache: Optional[torch.Tensor], slot_mapping: torch.Tensor, n_head: int, n_kv_head: int, dim: int, vdim: int,
+                     padded: int, page_size: int, norm_mode: int, eps: float, positions: torch.Tensor, freq: Optional[torch.Tensor], rot_dims: int,
+                     v_first_in: Optional[torch.Tensor] = None, v_first_out: Optional[torch.Tensor] = None, blend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Queries, keys and values of a float projection on their way to attention: norm_mode 0 none, 1 a head, 2 the whole projection; the first
+    rot_dims values of every head rotated by positions[t] * freq[i]; values blended with v_first_in by blend[0], or left in v_first_out."""
+    shared = v_first_in if v_first_in is not None else v_first_out
+    check(lib().lb_qkv_rotary_store(_code(q_out.dtype, "q_out"), _dev(proj, "proj", torch.float32), proj.stride(0), q_off, k_off, v_off,
+                                    _opt(q_weight, "q_weight", torch.float32), _opt(k_weight, "k_weight", torch.float32), _dev(q_out, "q_out"), q_out.stride(0),
+                                    _opt(cache, "cache", q_out.dtype), _dev(slot_mapping, "slot_mapping", torch.int32), proj.shape[0], n_head, n_kv_head, dim, vdim,
+                                    padded, page_size, norm_mode, float(eps), _dev(positions, "positions", torch.int32), _opt(freq, "freq", torch.float32), rot_dims,
+                                    _opt(v_first_in, "v_first_in", torch.float32), _opt(v_first_out, "v_first_out", torch.float32),
+                                    shared.stride(0) if shared is not None else 0, _opt(blend, "blend", torch.float32), stream_ptr()), "qkv_rotary_store")
+    return q_out
+
+
+def row_norm_gate(o: torch.Tensor, g: Optional[torch.Tensor], gain: Optional[torch.Tensor], out: torch.Tensor, gate: str, eps: float) -> torch.Tensor:
+    """out = o over the root mean square of the whole row, times gain, times gate(g) (sigmoid or silu)."""
+    check(lib().lb_row_norm_gate(_code(out.dtype, "out"), _dev(o, "o", torch.float32), o.stride(0), _opt(g, "g", torch.float32), g.stride(0) if g is not None else 0,
+                                 _opt(gain, "gain", torch.float32), _dev(out, "out"), out.stride(0), o.shape[0], o.shape[1], {"sigmoid": 0, "silu": 1}[gate],
+                                 float(eps), stream_ptr()), "row_norm_gate")
+    return out
+
+
+def activate_columns(x: torch.Tensor, cols: int, gate: str) -> torch.Tensor:
+    """In place over the first `cols` columns of the float rows x: sigmoid, silu, gelu_tanh or relu."""
+    check(lib().lb_activate_columns(_dev(x, "x", torch.float32), x.stride(0), x.shape[0], cols, {"sigmoid": 0, "silu": 1, "gelu_tanh": 2, "relu": 3}[gate],
+                                    stream_ptr()), "activate_columns")
+    return x
+
+
+def router_table(tokens: torch.Tensor, table: torch.Tensor, n_experts: int):
+    """(ids [T, top] int32, weights [T, top] float32): the experts of every row from the table's row of its token id, each weighing 1 / top."""
+    T, top = tokens.shape[0], table.shape[1]
+    ids = torch.empty(T, top, dtype=torch.int32, device=tokens.device)
+    weights = torch.empty(T, top, dtype=torch.float32, device=tokens.device)
+    check(lib().lb_router_table(_dev(tokens, "tokens", torch.int32), _dev(table, "table", torch.int32), _dev(ids, "ids"), _dev(weights, "weights"), T, top,
+                                n_experts, table.shape[0], stream_ptr()), "router_table")
+    return ids, weights

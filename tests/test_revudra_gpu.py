@@ -259,8 +259,8 @@ def test_sinks_rotation_blend_and_norm_show(tmp_path):
     assert moved_rows(swapped("rms_norm", per_head), want) >= 50, "the norm over the whole projection does not show"
     reqs = {"a": toks}
     for steps in (tt.whole(reqs), tt.tail_one_by_one(reqs, 100), tt.changing_portions(reqs, sizes=(6, 1, 7, 2, 8, 13, 64))):
-        for dtype in ("float32", "bfloat16"):
-            check(tt.collect(make_engine(path, dtype, max_tokens=192), steps), {"a": want}, dtype)
+        for dtype in ("float32", "bfloat16"):       # scores this sharp double what a rounding of a query or key costs
+            check(tt.collect(make_engine(path, dtype, max_tokens=192), steps), {"a": want}, dtype, worst=0.12)
 
 
 def test_far_keys_and_memories_that_reach_far_back(tmp_path):
