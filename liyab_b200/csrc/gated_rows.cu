@@ -95,6 +95,54 @@ __global__ void rms_sum_add_kernel(float* __restrict__ x, int64_t ldx, Branches 
     }
 }
 
+// One branch, rows of up to 128 * NV values that split into 16-byte pieces: a warp per row.  The row of y, the row of x and the gains are
+// all asked for at once (16 bytes a lane and piece), the sum of squares meets by shuffles, and the sums go back without a block-wide barrier;
+// a step of a few rows is then two round trips to memory, and a step of thousands streams at the copy rate.
+template <int NV>
+__global__ void __launch_bounds__(128) rms_add_warp_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, int64_t ldy,
+                                                           const float* __restrict__ w, int n_rows, int width, float scale, float eps,
+                                                           __nv_bfloat16* __restrict__ x16, int64_t ld16) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int lane = threadIdx.x & 31, r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int pieces = width >> 2;
+    const float4* yr = reinterpret_cast<const float4*>(y + (size_t)r * ldy);
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)r * ldx);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    float4 yv[NV], xv[NV], wv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int p = lane + 32 * i;
+        const bool in = p < pieces;
+        yv[i] = in ? yr[p] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        xv[i] = in ? xr[p] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        wv[i] = in && w != nullptr ? wr[p] : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) ss = fmaf(yv[i].x, yv[i].x, fmaf(yv[i].y, yv[i].y, fmaf(yv[i].z, yv[i].z, fmaf(yv[i].w, yv[i].w, ss))));
+    const float f = scale / sqrtf(lb_warp_sum(ss) / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int p = lane + 32 * i;
+        if (p >= pieces) break;
+        float4 o;
+        o.x = fmaf(yv[i].x * f, wv[i].x, xv[i].x);
+        o.y = fmaf(yv[i].y * f, wv[i].y, xv[i].y);
+        o.z = fmaf(yv[i].z * f, wv[i].z, xv[i].z);
+        o.w = fmaf(yv[i].w * f, wv[i].w, xv[i].w);
+        xr[p] = o;
+        if (x16 != nullptr) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(x16 + (size_t)r * ld16 + 4 * p) = pk;
+        }
+    }
+}
+
 // ---------------------------------------------------------------- queries and keys normalised per head; keys and values to the cache
 // A block per token.  From the float row [.. q (H x D) .. k (G x D) .. v (G x E) ..]: every query head over its root mean
 // square times qw into the query rows [H x P] (P >= D, E; the rest zeros), every key head the same with kw into the K plane
@@ -221,6 +269,22 @@ extern "C" int lb_rms_sum_add_rounded(float* x, int64_t ldx, int n_branches, con
                                       int n_rows, int width, float scale, float eps, void* x16, int64_t ld16, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && width > 0 && n_branches >= 1 && n_branches <= 4, "rms_sum_add: %d branches (1 to 4)", n_branches);
     if (n_rows == 0) return LB_OK;
+    // One branch whose rows split into 16-byte pieces: a warp a row.
+    if (n_branches == 1 && width % 4 == 0 && width <= 2048 && ldx % 4 == 0 && ldy[0] % 4 == 0 && ld16 % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y[0]) | reinterpret_cast<uintptr_t>(weight != nullptr ? weight[0] : nullptr)) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(x16) & 7) == 0) {
+        const float* w = weight != nullptr ? weight[0] : nullptr;
+        const dim3 grid((unsigned)((n_rows + 3) / 4)), block(128);
+        auto s = static_cast<cudaStream_t>(stream);
+        auto x16p = static_cast<__nv_bfloat16*>(x16);
+#define LB_WARP_ROWS(NV) LB_CHECK_CUDA(lb_launch_overlapped(rms_add_warp_kernel<NV>, grid, block, 0, s, x, ldx, y[0], ldy[0], w, n_rows, width, scale, eps, x16p, ld16))
+        if (width <= 256) LB_WARP_ROWS(2);
+        else if (width <= 512) LB_WARP_ROWS(4);
+        else if (width <= 1024) LB_WARP_ROWS(8);
+        else LB_WARP_ROWS(16);
+#undef LB_WARP_ROWS
+        return LB_OK;
+    }
     Branches b{};
     b.n = n_branches;
     for (int i = 0; i < n_branches; ++i) {

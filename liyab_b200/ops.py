@@ -635,6 +635,7 @@ for _name, _args in {
     "lb_rms_groups_offset": [_i, _p, _l, _p, _p, _f, _p, _l, _i, _i, _i, _f, _p],
     "lb_add_row": [_p, _l, _p, _i, _i, _p],
     "lb_rms_sum_add": [_p, _l, _i, _p, _p, _p, _i, _i, _f, _f, _p],
+    "lb_rms_sum_add_rounded": [_p, _l, _i, _p, _p, _p, _i, _i, _f, _f, _p, _l, _p],
     "lb_qk_norm_store": [_i, _p, _l, _i, _i, _i, _p, _p, _p, _l, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
     "lb_head_gate": [_i, _i, _p, _l, _i, _p, _l, _p, _p, _l, _i, _i, _i, _i, _i, _f, _p],
     "lb_gated_act": [_i, _p, _l, _p, _l, _i, _i, _i, _p],
@@ -665,13 +666,15 @@ def add_row(x: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def rms_sum_add(x: torch.Tensor, branches, weights, scale: float, eps: float) -> torch.Tensor:
-    """x[r] += scale * sum_i rms(branches[i][r]) * weights[i] (float32 rows; a weight may be None)."""
+def rms_sum_add(x: torch.Tensor, branches, weights, scale: float, eps: float, rounded: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[r] += scale * sum_i rms(branches[i][r]) * weights[i] (float32 rows; a weight may be None); with `rounded` (bfloat16 rows) the new rows of
+    x are left there as well."""
     n = len(branches)
     ys = (_c.c_void_p * n)(*[_dev(y, "branch", torch.float32) for y in branches])
     ld = (_c.c_int64 * n)(*[y.stride(0) for y in branches])
     ws = (_c.c_void_p * n)(*[_opt(w, "weight", torch.float32) for w in weights])
-    check(lib().lb_rms_sum_add(_dev(x, "x", torch.float32), x.stride(0), n, ys, ld, ws, x.shape[0], x.shape[1], float(scale), float(eps), stream_ptr()), "rms_sum_add")
+    check(lib().lb_rms_sum_add_rounded(_dev(x, "x", torch.float32), x.stride(0), n, ys, ld, ws, x.shape[0], x.shape[1], float(scale), float(eps),
+                                       _opt(rounded, "rounded", torch.bfloat16), rounded.stride(0) if rounded is not None else 0, stream_ptr()), "rms_sum_add")
     return x
 
 

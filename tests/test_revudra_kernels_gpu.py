@@ -204,6 +204,28 @@ def test_norm_over_all_heads_with_a_gate(dev, dtype, width, gate):
     assert np.abs(out.double().cpu().numpy() - ref).max() < (1e-5 if dtype == torch.float32 else 1.5e-2) * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("width,rows", [(192, 8), (768, 300), (100, 5), (98, 3), (2048, 9), (4100, 2), (4, 1)])
+def test_sublayer_output_normed_and_added_to_the_stream(dev, width, rows):
+    """x += m y / rms(y) * w, with the new rows also rounded for the part that reads the stream next: widths that take the warp-a-row form
+    and ones that do not (no multiple of four, more than 2048 values), rows that start off 16 bytes, one row and hundreds."""
+    from liyab_b200 import ops
+    rng = np.random.default_rng(width + rows)
+    x, y, w = rng.standard_normal((rows, width + 4)), rng.standard_normal((rows, width)) * 2.0, rng.uniform(0.5, 1.5, width)
+    eps, m = 1e-5, 0.7
+    ref = x[:, :width] + m * y / np.sqrt((y * y).mean(-1, keepdims=True) + eps) * w
+    t = lambda a: torch.tensor(a, dtype=torch.float32, device=dev)
+    for offset in (0, 1):          # rows that start on 16 bytes, and ones that do not
+        xs = t(x)[:, offset:offset + width] if offset else t(x)[:, :width]
+        want = ref if not offset else x[:, offset:offset + width] + (ref - x[:, :width])
+        rounded = torch.full((rows, width), float("nan"), dtype=torch.bfloat16, device=dev)
+        ops.rms_sum_add(xs, [t(y)], [t(w)], m, eps, rounded=rounded)
+        assert np.abs(xs.double().cpu().numpy() - want).max() < 1e-5 * max(1.0, np.abs(want).max())
+        assert (rounded.float() == xs.to(torch.bfloat16).float()).all()
+        xs = t(x)[:, :width]
+        ops.rms_sum_add(xs, [t(y)], [None], m, eps)
+        assert np.abs(xs.double().cpu().numpy() - (x[:, :width] + m * y / np.sqrt((y * y).mean(-1, keepdims=True) + eps))).max() < 1e-5 * max(1.0, np.abs(ref).max())
+
+
 def test_activation_over_some_columns(dev):
     from liyab_b200 import ops
     rng = np.random.default_rng(3)
