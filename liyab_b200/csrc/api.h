@@ -481,6 +481,9 @@ int lb_latent_attention_mma_ext(const void* wide, int64_t ldw, const void* cache
  * reads the stream next. */
 int lb_rms_sum_add_rounded(float* x, int64_t ldx, int n_branches, const float* const* y, const int64_t* ldy, const float* const* weight, int n_rows,
                            int width, float scale, float eps, void* x16, int64_t ld16, void* stream);
+/* lb_router_table and lb_expert_plan in one launch: ids and weights [n_rows, top] are filled from the table, then the plan is made from them. */
+int lb_expert_plan_table(const int32_t* tokens, const int32_t* table, int vocab, int top, int32_t* ids, float* weights, int n_rows, int n_experts,
+                         int32_t* offsets, int32_t* place, int32_t* pair_at, void* stream);
 /* lb_expert_combine_weighted that, with `overwrite`, writes the rows' sums to x instead of adding them. */
 int lb_expert_combine_into(float* x, int64_t ldx, const float* y, int64_t ldy, const int32_t* place, const float* weights, int n_rows, int width, int top,
                            int overwrite, void* stream);

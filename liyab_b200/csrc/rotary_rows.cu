@@ -24,24 +24,37 @@ __global__ void qkv_rotary_store_kernel(const float* __restrict__ proj, int64_t 
                                         const int32_t* __restrict__ slot_mapping, int H, int G, int D, int E, int P, int page_size, int norm_mode, float eps,
                                         const int32_t* __restrict__ positions, const float* __restrict__ freq, int rot_dims,
                                         const float* __restrict__ v_first_in, float* __restrict__ v_first_out, int64_t ldv, const float* __restrict__ lambda) {
-    __shared__ float scratch[33];
+    __shared__ float red[2][32];
+    extern __shared__ float turn[];            // [rot_dims]: cosine then sine of every pair's angle, made once for all heads of the token
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const float* row = proj + (size_t)t * ld;
+    // What the rest waits for is asked for together: the position, the slot, the blend's weight and the rows' values for the two sums.
     const int pos = positions != nullptr ? positions[t] : 0;
+    const int slot = cache != nullptr ? slot_mapping[t] : -1;
+    const float lam = v_first_in != nullptr ? lambda[0] : 0.0f;
     const int half = rot_dims / 2;
-    float inv_q = 1.0f, inv_k = 1.0f;
+    float sq = 0.0f, sk = 0.0f;
     if (norm_mode == 2) {
-        float sq = 0.0f, sk = 0.0f;
         for (int i = threadIdx.x; i < H * D; i += blockDim.x) sq = fmaf(row[q_off + i], row[q_off + i], sq);
         for (int i = threadIdx.x; i < G * D; i += blockDim.x) sk = fmaf(row[k_off + i], row[k_off + i], sk);
-        inv_q = 1.0f / sqrtf(lb_block_sum(sq, scratch) / (float)(H * D) + eps);
-        inv_k = 1.0f / sqrtf(lb_block_sum(sk, scratch) / (float)(G * D) + eps);
     }
-    const int slot = cache != nullptr ? slot_mapping[t] : -1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * freq[i], &turn[half + i], &turn[i]);
+    // Both sums of squares meet behind one barrier (which also makes the angles visible); every thread adds the warps' shares
+    // in the same order.
+    sq = lb_warp_sum(sq);
+    sk = lb_warp_sum(sk);
+    if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+    __syncthreads();
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (norm_mode == 2) {
+        float tq = 0.0f, tk = 0.0f;
+        for (int w = 0; w < n_warps; ++w) { tq += red[0][w]; tk += red[1][w]; }
+        inv_q = 1.0f / sqrtf(tq / (float)(H * D) + eps);
+        inv_k = 1.0f / sqrtf(tk / (float)(G * D) + eps);
+    }
     const size_t plane = (size_t)G * page_size * P;
-    const float lam = v_first_in != nullptr ? lambda[0] : 0.0f;
     for (int job = warp; job < H + 2 * G; job += n_warps) {
         if (job >= H + G) {                     // a value head
             const int g = job - H - G;
@@ -91,8 +104,7 @@ __global__ void qkv_rotary_store_kernel(const float* __restrict__ proj, int64_t 
             if (d < D) {
                 if (d < rot_dims) {
                     const int i = d < half ? d : d - half;
-                    float sn, cs;
-                    sincosf((float)pos * freq[i], &sn, &cs);
+                    const float cs = turn[i], sn = turn[half + i];
                     const float lo = normed(i), hi = normed(i + half);
                     v = d < half ? lo * cs - hi * sn : hi * cs + lo * sn;
                 } else {
@@ -193,13 +205,15 @@ extern "C" int lb_qkv_rotary_store(int dtype, const float* proj, int64_t ld, int
     LB_CHECK_ARG(v_first_in == nullptr || lambda != nullptr, "qkv_rotary_store: a blend of values needs its weight");
     if (n_tokens == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
-    const int jobs = n_head + 2 * n_kv_head, threads = 32 * min(8, jobs);
+    // A warp a head where a block holds them all (a step of few tokens is then one pass); eight warps in turn for steps of many tokens.
+    const int jobs = n_head + 2 * n_kv_head, threads = 32 * min(n_tokens <= 64 ? 32 : 8, jobs);
+    const size_t smem = (size_t)max(rot_dims, 1) * sizeof(float);
     if (dtype == LB_F32)
-        LB_CHECK_CUDA(lb_launch_overlapped(qkv_rotary_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, proj, ld, q_off, k_off, v_off, q_weight, k_weight,
+        LB_CHECK_CUDA(lb_launch_overlapped(qkv_rotary_store_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, proj, ld, q_off, k_off, v_off, q_weight, k_weight,
                                            (float*)q_out, ldq, (float*)cache, slot_mapping, n_head, n_kv_head, dim, vdim, padded, page_size, norm_mode, eps,
                                            positions, freq, rot_dims, v_first_in, v_first_out, ldv, lambda));
     else if (dtype == LB_BF16)
-        LB_CHECK_CUDA(lb_launch_overlapped(qkv_rotary_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, proj, ld, q_off, k_off, v_off, q_weight,
+        LB_CHECK_CUDA(lb_launch_overlapped(qkv_rotary_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem, s, proj, ld, q_off, k_off, v_off, q_weight,
                                            k_weight, (__nv_bfloat16*)q_out, ldq, (__nv_bfloat16*)cache, slot_mapping, n_head, n_kv_head, dim, vdim, padded,
                                            page_size, norm_mode, eps, positions, freq, rot_dims, v_first_in, v_first_out, ldv, lambda));
     else return lb_fail(LB_ERR_INVALID_ARGUMENT, "qkv_rotary_store: unknown dtype %d", dtype);

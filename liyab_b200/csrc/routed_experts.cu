@@ -70,12 +70,24 @@ __global__ void router_topk_kernel(const T* __restrict__ h, int64_t ldh, const T
 
 // ---------------------------------------------------------------- plan
 // offsets [E + 1]; place[pair] = where the pair stands in the sorted order; pair_at[place] = the pair.
-__global__ void __launch_bounds__(1024) expert_plan_kernel(const int32_t* __restrict__ ids_global, int n_pairs, int E, int32_t* __restrict__ offsets,
-                                                           int32_t* __restrict__ place, int32_t* __restrict__ pair_at, int staged) {
+// With `tokens` and `table` (int32 [vocab, top]) the pairs' experts are first looked up by the rows' token ids, pair (r, j) -> table[tokens[r]][j],
+// left in ids_global, and every pair's weight 1 / top in `weights`: the routing without a router, in the plan's own launch.
+__global__ void __launch_bounds__(1024) expert_plan_kernel(int32_t* __restrict__ ids_global, int n_pairs, int E, int32_t* __restrict__ offsets,
+                                                           int32_t* __restrict__ place, int32_t* __restrict__ pair_at, int staged,
+                                                           const int32_t* __restrict__ tokens, const int32_t* __restrict__ table, int vocab, int top,
+                                                           float* __restrict__ weights) {
     extern __shared__ int counts[];    // [E + 1], then the pairs' experts where they fit (`staged`)
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    if (tokens != nullptr) {
+        for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+            const int r = p / top, tok = min(max(tokens[r], 0), vocab - 1);
+            ids_global[p] = min(max(table[(size_t)tok * top + (p - r * top)], 0), E - 1);      // an entry outside the experts is kept inside
+            weights[p] = 1.0f / (float)top;
+        }
+        __syncthreads();                // the block's own writes are what it reads below
+    }
     // Every warp walks all pairs twice: from shared memory where they fit, so that a walk is not a chain of round trips.
     const int32_t* ids = ids_global;
     if (staged) {
@@ -557,7 +569,20 @@ extern "C" int lb_expert_plan(const int32_t* ids, int n_pairs, int n_experts, in
     const int threads = 32 * max(1, min(32, n_experts));
     const int staged = (size_t)(n_experts + 1 + n_pairs) * sizeof(int) <= 48 * 1024 ? 1 : 0;
     LB_CHECK_CUDA(lb_launch_overlapped(expert_plan_kernel, dim3(1), dim3(threads), (size_t)(n_experts + 1 + (staged ? n_pairs : 0)) * sizeof(int),
-                                       static_cast<cudaStream_t>(stream), ids, n_pairs, n_experts, offsets, place, pair_at, staged));
+                                       static_cast<cudaStream_t>(stream), const_cast<int32_t*>(ids), n_pairs, n_experts, offsets, place, pair_at, staged,
+                                       (const int32_t*)nullptr, (const int32_t*)nullptr, 0, 1, (float*)nullptr));
+    return LB_OK;
+}
+
+extern "C" int lb_expert_plan_table(const int32_t* tokens, const int32_t* table, int vocab, int top, int32_t* ids, float* weights, int n_rows, int n_experts,
+                                    int32_t* offsets, int32_t* place, int32_t* pair_at, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && n_experts > 0 && n_experts <= 4096 && top > 0 && vocab > 0, "expert plan by table: bad sizes");
+    const int n_pairs = n_rows * top;
+    const int threads = 32 * max(1, min(32, n_experts));
+    const int staged = (size_t)(n_experts + 1 + n_pairs) * sizeof(int) <= 48 * 1024 ? 1 : 0;
+    LB_CHECK_CUDA(lb_launch_overlapped(expert_plan_kernel, dim3(1), dim3(threads), (size_t)(n_experts + 1 + (staged ? n_pairs : 0)) * sizeof(int),
+                                       static_cast<cudaStream_t>(stream), ids, n_pairs, n_experts, offsets, place, pair_at, staged, tokens, table, vocab, top,
+                                       weights));
     return LB_OK;
 }
 

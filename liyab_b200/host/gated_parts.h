@@ -559,9 +559,12 @@ public:
         int32_t* place = static_cast<int32_t*>(ws.get("routed.place", T, top, DType::I32).data);
         int32_t* pair_at = static_cast<int32_t*>(ws.get("routed.pair_at", T, top, DType::I32).data);
         int32_t* offsets = static_cast<int32_t*>(ws.flat("routed.offsets", experts + 1, DType::I32));
-        if (by_table) kernels::router_table(s, ctx.tokens, table, ids, weights, T, top, experts);
-        else kernels::router_topk(s, h, router, ids, weights, T, top, softmax, renormalise, router_bias);
-        kernels::expert_plan(s, ids, pairs, experts, offsets, place, pair_at);
+        if (by_table) {       // the look-up rides in the plan's launch
+            kernels::expert_plan_table(s, ctx.tokens, table, ids, weights, T, top, experts, offsets, place, pair_at);
+        } else {
+            kernels::router_topk(s, h, router, ids, weights, T, top, softmax, renormalise, router_bias);
+            kernels::expert_plan(s, ids, pairs, experts, offsets, place, pair_at);
+        }
         Rows mid = ws.get("routed.inner", T, static_cast<int64_t>(top) * inner, ctx.runtime.dtype);
         mid = Rows{mid.data, mid.dtype, static_cast<int64_t>(pairs), inner, inner};
         Rows y = ws.get("routed.out", T, static_cast<int64_t>(top) * hidden, DType::F32);

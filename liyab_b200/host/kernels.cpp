@@ -388,6 +388,13 @@ void router_table(cudaStream_t s, const int32_t* tokens, const Tensor& table, in
     check(lb_router_table(tokens, static_cast<const int32_t*>(table.data), ids, weights, n_rows, top, n_experts, static_cast<int>(table.dim(0)), s), "router_table");
 }
 
+void expert_plan_table(cudaStream_t s, const int32_t* tokens, const Tensor& table, int32_t* ids, float* weights, int n_rows, int top, int n_experts,
+                       int32_t* offsets, int32_t* place, int32_t* pair_at) {
+    if (table.dtype != DType::I32 || table.shape.size() != 2 || table.dim(1) != top) throw invalid_argument("router table: an int32 table [vocab, top]");
+    check(lb_expert_plan_table(tokens, static_cast<const int32_t*>(table.data), static_cast<int>(table.dim(0)), top, ids, weights, n_rows, n_experts, offsets,
+                               place, pair_at, s), "expert_plan_table");
+}
+
 void rows_to_bf16(cudaStream_t s, const Rows& x, const Rows& y, int n_rows) {
     if (x.dtype != DType::F32 || y.dtype != DType::BF16 || x.cols != y.cols) throw invalid_argument("rows_to_bf16: float32 rows into bfloat16 rows of the same width");
     check(lb_rows_to_bf16(x.f32(), x.stride, y.data, y.stride, n_rows, static_cast<int>(x.cols), s), "rows_to_bf16");

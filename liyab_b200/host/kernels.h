@@ -201,6 +201,9 @@ void row_norm_gate(cudaStream_t s, const Rows& o, const Rows& g, const float* ga
 void activate_columns(cudaStream_t s, const Rows& x, int n_rows, int gate);
 // A row's experts looked up by its token id in an int32 table [vocab, top]; every weight 1 / top.
 void router_table(cudaStream_t s, const int32_t* tokens, const Tensor& table, int32_t* ids, float* weights, int n_rows, int top, int n_experts);
+// router_table and expert_plan in one launch.
+void expert_plan_table(cudaStream_t s, const int32_t* tokens, const Tensor& table, int32_t* ids, float* weights, int n_rows, int top, int n_experts,
+                       int32_t* offsets, int32_t* place, int32_t* pair_at);
 void rows_to_bf16(cudaStream_t s, const Rows& x, const Rows& y, int n_rows);
 // kCapped has two numbers (alpha, limit): g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1).
 enum Gate : int { kSigmoid = 0, kSilu = 1, kGeluGate = 2, kRelu = 3, kCapped = 4 };
