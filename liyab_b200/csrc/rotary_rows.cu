@@ -206,7 +206,7 @@ extern "C" int lb_qkv_rotary_store(int dtype, const float* proj, int64_t ld, int
     if (n_tokens == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
     // A warp a head where a block holds them all (a step of few tokens is then one pass); eight warps in turn for steps of many tokens.
-    const int jobs = n_head + 2 * n_kv_head, threads = 32 * min(n_tokens <= 64 ? 32 : 8, jobs);
+    const int jobs = n_head + 2 * n_kv_head, threads = 32 * min(n_tokens <= 64 ? 16 : 8, jobs);
     const size_t smem = (size_t)max(rot_dims, 1) * sizeof(float);
     if (dtype == LB_F32)
         LB_CHECK_CUDA(lb_launch_overlapped(qkv_rotary_store_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, proj, ld, q_off, k_off, v_off, q_weight, k_weight,
