@@ -559,8 +559,11 @@ public:
         int32_t* place = static_cast<int32_t*>(ws.get("routed.place", T, top, DType::I32).data);
         int32_t* pair_at = static_cast<int32_t*>(ws.get("routed.pair_at", T, top, DType::I32).data);
         int32_t* offsets = static_cast<int32_t*>(ws.flat("routed.offsets", experts + 1, DType::I32));
-        if (by_table) {       // the look-up rides in the plan's launch
+        if (by_table && pairs <= kLookupInPlan) {       // the look-up rides in the plan's launch (one block: worth it for steps of few rows)
             kernels::expert_plan_table(s, ctx.tokens, table, ids, weights, T, top, experts, offsets, place, pair_at);
+        } else if (by_table) {
+            kernels::router_table(s, ctx.tokens, table, ids, weights, T, top, experts);
+            kernels::expert_plan(s, ids, pairs, experts, offsets, place, pair_at);
         } else {
             kernels::router_topk(s, h, router, ids, weights, T, top, softmax, renormalise, router_bias);
             kernels::expert_plan(s, ids, pairs, experts, offsets, place, pair_at);
@@ -576,6 +579,9 @@ public:
         ctx.tap("routed", x);
         if (shared) shared->forward(ctx, h, x);
     }
+    // Up to this many (row, choice) pairs the table's look-up is part of the plan's launch (measured: 2.7 + 2.6 us as two launches against 3.9 us
+    // for 16 pairs; 16.6 + 3.5 us against 25.3 us for 4,096).
+    static constexpr int kLookupInPlan = 1024;
     int64_t hidden, inner;
     int experts, top, gate;
     bool renormalise, softmax = false, weight_on_output = false, by_table = false;
