@@ -161,6 +161,66 @@ __global__ void row_norm_gate_kernel(const float* __restrict__ o, int64_t ldo, c
     }
 }
 
+// The same for rows of up to 128 * NV values that split into 16-byte pieces: a warp a row, the row, its gates and the gains asked for at
+// once, the sum of squares by shuffles, no block-wide barrier.
+template <typename TO, int NV>
+__global__ void __launch_bounds__(128) row_norm_gate_warp_kernel(const float* __restrict__ o, int64_t ldo, const float* __restrict__ g, int64_t ldg,
+                                                                 const float* __restrict__ gain, TO* __restrict__ out, int64_t ld_out, int n_rows, int width,
+                                                                 int act, float eps) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const int lane = threadIdx.x & 31, r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int pieces = width >> 2;
+    const float4* orow = reinterpret_cast<const float4*>(o + (size_t)r * ldo);
+    const float4* grow = g != nullptr ? reinterpret_cast<const float4*>(g + (size_t)r * ldg) : nullptr;
+    const float4* wrow = reinterpret_cast<const float4*>(gain);
+    float4 ov[NV], gv[NV], wv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int p = lane + 32 * i;
+        const bool in = p < pieces;
+        ov[i] = in ? orow[p] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        gv[i] = in && grow != nullptr ? grow[p] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        wv[i] = in && gain != nullptr ? wrow[p] : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) ss = fmaf(ov[i].x, ov[i].x, fmaf(ov[i].y, ov[i].y, fmaf(ov[i].z, ov[i].z, fmaf(ov[i].w, ov[i].w, ss))));
+    const float inv = 1.0f / sqrtf(lb_warp_sum(ss) / (float)width + eps);
+    auto gate = [&](float z) { return grow == nullptr ? 1.0f : act == LB_GATE_SILU ? z * rr_sigmoid(z) : rr_sigmoid(z); };
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int p = lane + 32 * i;
+        if (p >= pieces) break;
+        const float a = ov[i].x * inv * wv[i].x * gate(gv[i].x), b = ov[i].y * inv * wv[i].y * gate(gv[i].y);
+        const float c = ov[i].z * inv * wv[i].z * gate(gv[i].z), d = ov[i].w * inv * wv[i].w * gate(gv[i].w);
+        TO* dst = out + (size_t)r * ld_out + 4 * p;
+        if constexpr (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst) = pk;
+        }
+    }
+}
+
+template <typename TO>
+int launch_row_norm_gate_warp(const float* o, int64_t ldo, const float* g, int64_t ldg, const float* gain, TO* out, int64_t ld_out, int n_rows, int width, int act,
+                              float eps, cudaStream_t s) {
+    const dim3 grid((unsigned)((n_rows + 3) / 4)), block(128);
+#define LB_WARP_ROWS(NV) LB_CHECK_CUDA(lb_launch_overlapped(row_norm_gate_warp_kernel<TO, NV>, grid, block, 0, s, o, ldo, g, ldg, gain, out, ld_out, n_rows, width, act, eps))
+    if (width <= 256) LB_WARP_ROWS(2);
+    else if (width <= 512) LB_WARP_ROWS(4);
+    else if (width <= 1024) LB_WARP_ROWS(8);
+    else LB_WARP_ROWS(16);
+#undef LB_WARP_ROWS
+    return LB_OK;
+}
+
 // ---------------------------------------------------------------- x[r, c] = act(x[r, c]) for c < cols, in place
 __device__ __forceinline__ float rr_activate(float z, int act) {
     return act == LB_GATE_SILU ? z * rr_sigmoid(z) : act == LB_GATE_GELU_TANH ? lb_gelu_tanh(z) : act == LB_GATE_RELU ? fmaxf(z, 0.0f) : rr_sigmoid(z);
@@ -238,6 +298,11 @@ extern "C" int lb_row_norm_gate(int out_dtype, const float* o, int64_t ldo, cons
     LB_CHECK_ARG(n_rows >= 0 && width > 0 && (act == LB_GATE_SIGMOID || act == LB_GATE_SILU), "row_norm_gate: bad sizes width=%d act=%d", width, act);
     if (n_rows == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
+    const uintptr_t places = reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(gain) | reinterpret_cast<uintptr_t>(out);
+    if (width % 4 == 0 && width <= 2048 && ldo % 4 == 0 && ldg % 4 == 0 && ld_out % 4 == 0 && (places & 15) == 0 && (out_dtype == LB_F32 || out_dtype == LB_BF16)) {
+        if (out_dtype == LB_F32) return launch_row_norm_gate_warp<float>(o, ldo, g, ldg, gain, (float*)out, ld_out, n_rows, width, act, eps, s);
+        return launch_row_norm_gate_warp<__nv_bfloat16>(o, ldo, g, ldg, gain, (__nv_bfloat16*)out, ld_out, n_rows, width, act, eps, s);
+    }
     const int threads = width > 512 ? 256 : 128;
     if (out_dtype == LB_F32)
         LB_CHECK_CUDA(lb_launch_overlapped(row_norm_gate_kernel<float>, dim3(n_rows), dim3(threads), 0, s, o, ldo, g, ldg, gain, (float*)out, ld_out, width, act, eps));

@@ -61,8 +61,8 @@ CONFIG_B = model(200, 128, 1e-6, 0.8, 0.5, 2.0, [
     layer(attention(4, 2, 64, 64, 0.125, 40, 32, 10000.0, True), moe(8, 2, 64)),
     layer(lightning(4, 32, 32, [0.7, 0.9, 0.97, 0.999]), dense(256)),
     layer(latent(4, 32, 16, 32, 64, 48, 0.14), moe(4, 1, 128)),
-    layer(attention(8, 2, 128, 64, 0.09, 48, 64, 1e6, True), dense(128)),
-    layer(latent(16, 16, 32, 16, 128, 96, 0.15, 20000.0), None),
+    layer(attention(8, 4, 128, 32, 0.09, 48, 32, 5e5, True), dense(128)),
+    layer(latent(16, 16, 32, 16, 128, 80, 0.15, 30000.0), None),
 ])
 CONFIG_C = model(97, 100, 1e-4, 1.0, 1.0, 1.0, [
     layer(latent(2, 6, 2, 70, 10, 5, 0.4), moe(3, 3, 20)),

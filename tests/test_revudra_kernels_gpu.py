@@ -49,7 +49,7 @@ def sinks(n_head, seed, dev):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window", [(4, 4, 16, 16, 0), (6, 2, 48, 32, 0), (5, 1, 64, 64, 70), (4, 2, 24, 16, 33), (2, 1, 64, 32, 7),
-                                                                        (8, 2, 128, 16, 72)])
+                                                                        (12, 3, 128, 16, 88)])
 def test_generic_attention_with_sinks(dev, dtype, n_head, n_kv_head, head_dim, page_size, window):
     from liyab_b200 import ops
     lens, q_lens = [1, 37, 130, 64, 300], [1, 37, 2, 1, 45]
@@ -68,7 +68,7 @@ def test_generic_attention_with_sinks(dev, dtype, n_head, n_kv_head, head_dim, p
 
 
 @pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window,splits", [
-    (12, 12, 64, 16, 0, 1), (12, 12, 64, 16, 0, 5), (4, 4, 16, 16, 0, 3), (8, 2, 128, 16, 72, 4), (16, 2, 64, 64, 0, 7), (6, 3, 64, 16, 33, 4),
+    (12, 12, 64, 16, 0, 1), (12, 12, 64, 16, 0, 5), (4, 4, 16, 16, 0, 3), (12, 3, 128, 16, 88, 4), (16, 2, 64, 64, 0, 7), (6, 3, 64, 16, 33, 4),
     (4, 4, 32, 16, 5, 16), (5, 5, 128, 32, 70, 2), (2, 1, 256, 16, 200, 9), (32, 2, 64, 16, 0, 3), (16, 1, 128, 16, 0, 8), (12, 3, 64, 16, 300, 12)])
 def test_decode_attention_with_sinks(dev, n_head, n_kv_head, head_dim, page_size, window, splits):
     """One new token per request, keys split several ways: the sink joins once, where the ranges meet, however many there are."""
@@ -95,7 +95,7 @@ def test_decode_attention_with_sinks(dev, n_head, n_kv_head, head_dim, page_size
 
 
 @pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window", [
-    (12, 12, 64, 16, 0), (4, 4, 16, 16, 0), (6, 2, 48, 32, 0), (5, 1, 64, 64, 0), (8, 2, 128, 16, 72), (4, 4, 32, 16, 40), (2, 1, 64, 32, 7), (3, 3, 64, 16, 100),
+    (12, 12, 64, 16, 0), (4, 4, 16, 16, 0), (6, 2, 48, 32, 0), (5, 1, 64, 64, 0), (12, 3, 128, 16, 88), (4, 4, 32, 16, 40), (2, 1, 64, 32, 7), (3, 3, 64, 16, 100),
     (6, 3, 64, 64, 75)])
 def test_prefill_attention_with_sinks(dev, n_head, n_kv_head, head_dim, page_size, window):
     """Prompt portions of every kind in one launch on both tensor-core kernels: a whole prompt, a portion that continues a long context,
@@ -122,7 +122,7 @@ def test_prefill_attention_with_sinks(dev, n_head, n_kv_head, head_dim, page_siz
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,E,rot,norm_mode,blend", [(4, 2, 12, 10, 8, 2, "blend"), (8, 2, 128, 48, 64, 2, "source"), (3, 3, 8, 8, 8, 1, None), (2, 1, 6, 9, 0, 2, "blend"),
+@pytest.mark.parametrize("H,G,D,E,rot,norm_mode,blend", [(4, 2, 12, 10, 8, 2, "blend"), (6, 2, 128, 40, 96, 2, "source"), (3, 3, 8, 8, 8, 1, None), (2, 1, 6, 9, 0, 2, "blend"),
                                                         (1, 1, 2, 1, 2, 0, None), (5, 5, 16, 4, 4, 2, None)])
 def test_queries_keys_and_values_on_their_way_to_the_cache(dev, dtype, H, G, D, E, rot, norm_mode, blend):
     """Norm over the whole projection (or a head, or none), rotation of part of a head at far positions, values blended or left for later
@@ -186,25 +186,27 @@ def test_queries_keys_and_values_on_their_way_to_the_cache(dev, dtype, H, G, D, 
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,gate", [(384, "sigmoid"), (60, "sigmoid"), (1, "silu"), (2050, "sigmoid"), (165, "silu")])
+@pytest.mark.parametrize("width,gate", [(320, "sigmoid"), (60, "sigmoid"), (1, "silu"), (2050, "sigmoid"), (165, "silu"), (2048, "silu"), (768, "sigmoid")])
 def test_norm_over_all_heads_with_a_gate(dev, dtype, width, gate):
+    """Rows that split into 16-byte pieces (a warp a row) and rows that do not (a block a row), with and without gains and gates."""
     from liyab_b200 import ops
     rng = np.random.default_rng(width)
     T, eps = 9, 1e-5
-    o, g, w = rng.standard_normal((T, width + 3)) * 3.0, rng.standard_normal((T, width)), rng.uniform(0.5, 1.5, width)
-    sig = 1.0 / (1.0 + np.exp(-g))
-    x = o[:, :width]
-    ref = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * w * (sig if gate == "sigmoid" else g * sig)
     t = lambda a: torch.tensor(a, dtype=torch.float32, device=dev)
-    out = torch.empty(T, width, dtype=dtype, device=dev)
-    ops.row_norm_gate(t(o)[:, :width], t(g), t(w), out, gate, eps)
-    assert np.abs(out.double().cpu().numpy() - ref).max() < (1e-5 if dtype == torch.float32 else 1.5e-2) * max(1.0, np.abs(ref).max())
-    ops.row_norm_gate(t(o)[:, :width], None, None, out, gate, eps)
-    ref = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
-    assert np.abs(out.double().cpu().numpy() - ref).max() < (1e-5 if dtype == torch.float32 else 1.5e-2) * max(1.0, np.abs(ref).max())
+    for pad in (3, 4):
+        o, g, w = rng.standard_normal((T, width + pad)) * 3.0, rng.standard_normal((T, width)), rng.uniform(0.5, 1.5, width)
+        sig = 1.0 / (1.0 + np.exp(-g))
+        x = o[:, :width]
+        ref = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * w * (sig if gate == "sigmoid" else g * sig)
+        out = torch.empty(T, width, dtype=dtype, device=dev)
+        ops.row_norm_gate(t(o)[:, :width], t(g), t(w), out, gate, eps)
+        assert np.abs(out.double().cpu().numpy() - ref).max() < (1e-5 if dtype == torch.float32 else 1.5e-2) * max(1.0, np.abs(ref).max())
+        ops.row_norm_gate(t(o)[:, :width], None, None, out, gate, eps)
+        ref = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
+        assert np.abs(out.double().cpu().numpy() - ref).max() < (1e-5 if dtype == torch.float32 else 1.5e-2) * max(1.0, np.abs(ref).max())
 
 
-@pytest.mark.parametrize("width,rows", [(192, 8), (768, 300), (100, 5), (98, 3), (2048, 9), (4100, 2), (4, 1)])
+@pytest.mark.parametrize("width,rows", [(160, 8), (768, 300), (100, 5), (98, 3), (2048, 9), (4100, 2), (4, 1)])
 def test_sublayer_output_normed_and_added_to_the_stream(dev, width, rows):
     """x += m y / rms(y) * w, with the new rows also rounded for the part that reads the stream next: widths that take the warp-a-row form
     and ones that do not (no multiple of four, more than 2048 values), rows that start off 16 bytes, one row and hundreds."""
@@ -237,7 +239,7 @@ def test_activation_over_some_columns(dev):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("m,n,k", [(3, 96, 64), (16, 384, 192), (70, 200, 128), (300, 3072, 768)])
+@pytest.mark.parametrize("m,n,k", [(3, 96, 64), (16, 320, 160), (70, 200, 128), (300, 3072, 768)])
 def test_square_of_relu_in_every_product(dev, dtype, m, n, k):
     """The chosen product kernel for few rows, dozens and hundreds (32-bit units, mma.sync rows, tcgen05 one tile and persistent)."""
     from liyab_b200 import ops
