@@ -191,9 +191,9 @@ def test_norm_over_all_heads_with_a_gate(dev, dtype, width, gate):
     """Rows that split into 16-byte pieces (a warp a row) and rows that do not (a block a row), with and without gains and gates."""
     from liyab_b200 import ops
     rng = np.random.default_rng(width)
-    T, eps = 9, 1e-5
+    eps = 1e-5
     t = lambda a: torch.tensor(a, dtype=torch.float32, device=dev)
-    for pad in (3, 4):
+    for pad, T in ((3, 9), (4, 9), (4, 70)):
         o, g, w = rng.standard_normal((T, width + pad)) * 3.0, rng.standard_normal((T, width)), rng.uniform(0.5, 1.5, width)
         sig = 1.0 / (1.0 + np.exp(-g))
         x = o[:, :width]
