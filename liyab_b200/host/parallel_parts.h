@@ -173,10 +173,16 @@ public:
         Rows q = qd.columns(0, q_cols);
         if (q_rank > 0) {
             // The queries' own latent: normed in 32-bit, then up to the heads.
-            const Rows cq = ws.get("latent.cq", T, q_rank, dt);
-            kernels::rms_groups(s, qd.columns(0, q_rank), nullptr, q_gain, cq, T, 1, eps);
             q = ws.get("latent.q_up", T, q_cols, DType::F32);
-            q_up.forward(ctx, cq, q, T);
+            const Rows down = qd.columns(0, q_rank);
+            if (q_up.bias == nullptr && kernels::gemm_rows_normed_supports(ctx.runtime, down, q_up.weight, T)) {
+                // A step of up to 16 tokens in bfloat16: the product normalises its rows itself, as the projections behind a norm do.
+                kernels::gemm_rows_normed(s, down, q_gain, nullptr, eps, q_up.weight, nullptr, q, T, kernels::kNone, nullptr, nullptr, true, 0.0f);
+            } else {
+                const Rows cq = ws.get("latent.cq", T, q_rank, dt);
+                kernels::rms_groups(s, down, nullptr, q_gain, cq, T, 1, eps);
+                q_up.forward(ctx, cq, q, T);
+            }
         }
         // bfloat16 and a shape the tensor-core kernel takes: wide queries in bfloat16 for it; else 32-bit throughout.
         const bool tensor = dt == DType::BF16 && kernels::latent_mma_supports(shape);
