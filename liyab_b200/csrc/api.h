@@ -477,6 +477,17 @@ int lb_latent_attention_mma_ext(const void* wide, int64_t ldw, const void* cache
                                 int n_seq, int max_q_len, int n_head, int rank, int rot, int page_size, float scale, int window, int n_splits,
                                 int merge_parts, const lb_latent_extras* extras, void* stream);
 
+/* lb_matrix_memory_shared / lb_matrix_memory_pieces_shared with an activation on queries, keys and values as the kernels read them
+ * (qkv_act: -1 none, 0 sigmoid, 1 silu, 2 GELU tanh form, 3 relu), before rotation and scales. */
+int lb_matrix_memory_activated(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                               const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
+                               int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
+                               float k_scale, float cap, int chunked, int qk_share, int qkv_act, void* stream);
+int lb_matrix_memory_pieces_activated(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                                      const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
+                                      int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq, int n_head, int dim, int vdim, int value_tile,
+                                      float q_scale, float k_scale, float cap, float* scratch, int qk_share, int qkv_act, void* stream);
+
 /* lb_rms_sum_add that also leaves the new rows of x rounded to bfloat16 in x16 (rows ld16 apart; null: as lb_rms_sum_add), for the part that
  * reads the stream next. */
 int lb_rms_sum_add_rounded(float* x, int64_t ldx, int n_branches, const float* const* y, const int64_t* ldy, const float* const* weight, int n_rows,

@@ -47,6 +47,7 @@ struct MemoryArgs {
     int H, D, E, VT, NV, rot_dims;
     float q_scale, k_scale, cap;
     int qk_share;              // heads that read one query and key row; 1: every head its own
+    int qkv_act;               // an activation on queries, keys and values as they arrive (0 sigmoid, 1 silu, 2 GELU tanh form, 3 relu); -1: none
 };
 
 // Scratch of the three-launch form for long prompts, in which every piece of 32 rows is a block of its own.
@@ -75,6 +76,12 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ float arriving(float z, int act) {
+    if (act < 0) return z;
+    const float sg = 1.0f / (1.0f + expf(-z));
+    return act == LB_GATE_SILU ? z * sg : act == LB_GATE_GELU_TANH ? lb_gelu_tanh(z) : act == LB_GATE_RELU ? fmaxf(z, 0.0f) : sg;
+}
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
 
@@ -165,7 +172,12 @@ __global__ void __launch_bounds__(256) matrix_memory_rows_kernel(MemoryArgs a, i
         __syncthreads();                   // the row has arrived; everyone is done with the row before
         if (row + 1 < row1) ask(row + 1, buffer ^ 1);
         cp_async_commit();
-        const float* mine = raw + buffer * raw_row;
+        float* mine = raw + buffer * raw_row;
+        if (a.qkv_act >= 0) {              // the row's queries, keys and (real) values pass the activation where they landed
+            for (int i = threadIdx.x; i < raw_row; i += blockDim.x)
+                if (i < 2 * D || nv * VT + (i - 2 * D) < E) mine[i] = arriving(mine[i], a.qkv_act);
+            __syncthreads();
+        }
         for (int d = threadIdx.x; d < 2 * D; d += blockDim.x) {
             const bool is_k = d >= D;
             const int dd = is_k ? d - D : d;
@@ -336,6 +348,17 @@ __global__ void __launch_bounds__(NT) matrix_memory_chunks_kernel(MemoryArgs a, 
         }
         cp_async_wait_all();
         __syncthreads();
+        if (a.qkv_act >= 0) {              // queries, keys and (real) values pass the activation where they landed
+            for (int t = warp; t < n; t += kWarps) {
+                for (int d = lane; d < D; d += 32) {
+                    if (MODE != 1) qs[t * LDQ + d] = arriving(qs[t * LDQ + d], a.qkv_act);
+                    ks[t * LDQ + d] = arriving(ks[t * LDQ + d], a.qkv_act);
+                }
+                for (int x = lane; x < VT; x += 32)
+                    if (nv * VT + x < E) vs[t * VT + x] = arriving(vs[t * VT + x], a.qkv_act);
+            }
+            __syncwarp();                  // the warp that activated a row is the one that rotates it below
+        }
         // Rotation and scales, in place.
         {
             const int half = a.rot_dims >> 1;
@@ -529,7 +552,8 @@ struct PieceScratch {
 static int matrix_memory_run(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
                              const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
                              int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
-                             float k_scale, float cap, int chunked, const PieceScratch* pieces, int qk_share, void* stream) {
+                             float k_scale, float cap, int chunked, const PieceScratch* pieces, int qk_share, int qkv_act, void* stream) {
+    LB_CHECK_ARG(qkv_act >= -1 && qkv_act <= LB_GATE_RELU, "matrix memory: activation %d on queries, keys and values (-1 none, 0 sigmoid, 1 silu, 2 gelu_tanh, 3 relu)", qkv_act);
     LB_CHECK_ARG(n_seq >= 0 && n_head > 0 && dim > 0 && vdim > 0 && value_tile > 0 && value_tile <= 64, "matrix memory: bad sizes heads=%d dim=%d vdim=%d tile=%d",
                  n_head, dim, vdim, value_tile);
     LB_CHECK_ARG(decay != nullptr ? (zi == nullptr && zf == nullptr) : zf != nullptr, "matrix memory: a fixed decay, or the two gates, or the log of a decay a token");
@@ -540,7 +564,7 @@ static int matrix_memory_run(const float* q, const float* k, const float* v, con
     a.q = q; a.k = k; a.v = v; a.zi = zi; a.zf = zf; a.ld = ld; a.decay = decay; a.freq = freq; a.positions = positions; a.q_start = q_start;
     a.slots = slots; a.state = state; a.slot_stride = slot_stride; a.out = out; a.ldo = ldo;
     a.H = n_head; a.D = dim; a.E = vdim; a.VT = value_tile; a.NV = (vdim + value_tile - 1) / value_tile; a.rot_dims = rot_dims;
-    a.q_scale = q_scale; a.k_scale = k_scale; a.cap = cap; a.qk_share = qk_share;
+    a.q_scale = q_scale; a.k_scale = k_scale; a.cap = cap; a.qk_share = qk_share; a.qkv_act = qkv_act;
     LB_CHECK_ARG(slot_stride >= (int64_t)n_head * a.NV * ((int64_t)dim * value_tile + dim + 1), "matrix memory: the state slots are too small");
     int p2 = 1;
     while (p2 < value_tile) p2 <<= 1;
@@ -582,15 +606,23 @@ extern "C" int lb_matrix_memory(const float* q, const float* k, const float* v, 
                                 int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
                                 float k_scale, float cap, int chunked, void* stream) {
     return matrix_memory_run(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim, vdim,
-                             value_tile, q_scale, k_scale, cap, chunked, nullptr, 1, stream);
+                             value_tile, q_scale, k_scale, cap, chunked, nullptr, 1, -1, stream);
 }
 
 extern "C" int lb_matrix_memory_shared(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
                                        const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots, float* state,
                                        int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile, float q_scale,
                                        float k_scale, float cap, int chunked, int qk_share, void* stream) {
+    return lb_matrix_memory_activated(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim,
+                                      vdim, value_tile, q_scale, k_scale, cap, chunked, qk_share, -1, stream);
+}
+
+extern "C" int lb_matrix_memory_activated(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,
+                                          const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots,
+                                          float* state, int64_t slot_stride, float* out, int64_t ldo, int n_seq, int n_head, int dim, int vdim, int value_tile,
+                                          float q_scale, float k_scale, float cap, int chunked, int qk_share, int qkv_act, void* stream) {
     return matrix_memory_run(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim, vdim,
-                             value_tile, q_scale, k_scale, cap, chunked, nullptr, qk_share, stream);
+                             value_tile, q_scale, k_scale, cap, chunked, nullptr, qk_share, qkv_act, stream);
 }
 
 extern "C" int64_t lb_matrix_memory_pieces_floats(int n_tokens, int n_seq, int n_head, int dim, int vdim, int value_tile) {
@@ -602,12 +634,21 @@ extern "C" int lb_matrix_memory_pieces_shared(const float* q, const float* k, co
                                               const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start, const int32_t* slots,
                                               float* state, int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq, int n_head, int dim, int vdim,
                                               int value_tile, float q_scale, float k_scale, float cap, float* scratch, int qk_share, void* stream) {
+    return lb_matrix_memory_pieces_activated(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_tokens, n_seq,
+                                             n_head, dim, vdim, value_tile, q_scale, k_scale, cap, scratch, qk_share, -1, stream);
+}
+
+extern "C" int lb_matrix_memory_pieces_activated(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld,
+                                                 const float* decay, const float* freq, int rot_dims, const int32_t* positions, const int32_t* q_start,
+                                                 const int32_t* slots, float* state, int64_t slot_stride, float* out, int64_t ldo, int n_tokens, int n_seq,
+                                                 int n_head, int dim, int vdim, int value_tile, float q_scale, float k_scale, float cap, float* scratch,
+                                                 int qk_share, int qkv_act, void* stream) {
     LB_CHECK_ARG(scratch != nullptr && n_tokens >= 0 && value_tile > 0, "matrix memory in pieces: no scratch");
     const int64_t pieces = n_tokens / 32 + n_seq, tiles = (vdim + value_tile - 1) / value_tile;
     const int64_t sums = pieces * n_head * tiles * ((int64_t)dim * value_tile + dim);
     const PieceScratch ps{scratch, scratch + sums, scratch + sums + pieces * n_head * 2, (int)pieces};
     return matrix_memory_run(q, k, v, zi, zf, ld, decay, freq, rot_dims, positions, q_start, slots, state, slot_stride, out, ldo, n_seq, n_head, dim, vdim,
-                             value_tile, q_scale, k_scale, cap, 1, &ps, qk_share, stream);
+                             value_tile, q_scale, k_scale, cap, 1, &ps, qk_share, qkv_act, stream);
 }
 
 extern "C" int lb_matrix_memory_pieces(const float* q, const float* k, const float* v, const float* zi, const float* zf, int64_t ld, const float* decay,

@@ -415,9 +415,9 @@ void matrix_memory(cudaStream_t s, const Rows& q, const Rows& k, const Rows& v, 
     if (q.dtype != DType::F32 || out.dtype != DType::F32 || k.stride != q.stride || v.stride != q.stride || (zi != nullptr && zi->stride != q.stride) ||
         (zf != nullptr && zf->stride != q.stride))
         throw invalid_argument("matrix memory: queries, keys, values and gates are column blocks of one float buffer");
-    check(lb_matrix_memory_shared(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay, freq,
-                                  m.rot_dims, positions, q_start, slots, state, m.stride(), out.f32(), out.stride, n_seq, m.n_head, m.dim, m.vdim,
-                                  m.value_tile, m.q_scale, m.k_scale, m.cap, chunked ? 1 : 0, m.qk_share, s), "matrix_memory");
+    check(lb_matrix_memory_activated(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay, freq,
+                                     m.rot_dims, positions, q_start, slots, state, m.stride(), out.f32(), out.stride, n_seq, m.n_head, m.dim, m.vdim,
+                                     m.value_tile, m.q_scale, m.k_scale, m.cap, chunked ? 1 : 0, m.qk_share, m.qkv_act, s), "matrix_memory");
 }
 
 int64_t memory_pieces_floats(int n_tokens, int n_seq, const MemoryShape& m) {
@@ -430,9 +430,9 @@ void matrix_memory_pieces(cudaStream_t s, const Rows& q, const Rows& k, const Ro
     if (q.dtype != DType::F32 || out.dtype != DType::F32 || k.stride != q.stride || v.stride != q.stride || (zi != nullptr && zi->stride != q.stride) ||
         (zf != nullptr && zf->stride != q.stride))
         throw invalid_argument("matrix memory: queries, keys, values and gates are column blocks of one float buffer");
-    check(lb_matrix_memory_pieces_shared(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay,
-                                         freq, m.rot_dims, positions, q_start, slots, state, m.stride(), out.f32(), out.stride, n_tokens, n_seq, m.n_head,
-                                         m.dim, m.vdim, m.value_tile, m.q_scale, m.k_scale, m.cap, scratch, m.qk_share, s), "matrix_memory_pieces");
+    check(lb_matrix_memory_pieces_activated(q.f32(), k.f32(), v.f32(), zi != nullptr ? zi->f32() : nullptr, zf != nullptr ? zf->f32() : nullptr, q.stride, decay,
+                                            freq, m.rot_dims, positions, q_start, slots, state, m.stride(), out.f32(), out.stride, n_tokens, n_seq, m.n_head,
+                                            m.dim, m.vdim, m.value_tile, m.q_scale, m.k_scale, m.cap, scratch, m.qk_share, m.qkv_act, s), "matrix_memory_pieces");
     launches.fetch_add(2, std::memory_order_relaxed);
 }
 

@@ -220,6 +220,7 @@ struct MemoryShape {
     int n_head = 0, dim = 0, vdim = 0, value_tile = 0, rot_dims = 0;
     float q_scale = 1.0f, k_scale = 1.0f, cap = 0.0f;
     int qk_share = 1;                // heads that read one query and key row (a group's); 1: every head its own
+    int qkv_act = -1;                // an activation on queries, keys and values as the kernels read them (a Gate code up to kRelu); -1: none
     int64_t slot_stride = 0;         // floats between two requests' states; 0: slot_floats() (a mixer may keep more in its slot)
     int64_t stride() const { return slot_stride > 0 ? slot_stride : slot_floats(); }
     int tiles() const { return (vdim + value_tile - 1) / value_tile; }

@@ -643,6 +643,8 @@ for _name, _args in {
     "lb_matrix_memory_pieces": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _i, _f, _f, _f, _p, _p],
     "lb_matrix_memory_shared": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _f, _f, _f, _i, _i, _p],
     "lb_matrix_memory_pieces_shared": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _i, _f, _f, _f, _p, _i, _p],
+    "lb_matrix_memory_activated": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _f, _f, _f, _i, _i, _i, _p],
+    "lb_matrix_memory_pieces_activated": [_p, _p, _p, _p, _p, _l, _p, _p, _i, _p, _p, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _i, _f, _f, _f, _p, _i, _i, _p],
     "lb_router_topk": [_i, _p, _l, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "lb_expert_plan": [_p, _i, _i, _p, _p, _p, _p],
     "lb_expert_product": [_i, _i, _p, _l, _p, _l, _p, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _p],
@@ -705,6 +707,9 @@ def gated_act(gu: torch.Tensor, out: torch.Tensor, gate: str) -> torch.Tensor:
     return out
 
 
+_QKV_ACT = {None: -1, "sigmoid": 0, "silu": 1, "gelu_tanh": 2, "relu": 3}
+
+
 def memory_slot_floats(n_head: int, dim: int, vdim: int, value_tile: int) -> int:
     return n_head * ((vdim + value_tile - 1) // value_tile) * (dim * value_tile + dim + 1)
 
@@ -712,24 +717,24 @@ def memory_slot_floats(n_head: int, dim: int, vdim: int, value_tile: int) -> int
 def matrix_memory(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, zi_off: Optional[int], zf_off: Optional[int], decay: Optional[torch.Tensor],
                   freq: Optional[torch.Tensor], rot_dims: int, positions: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
                   out: torch.Tensor, n_head: int, dim: int, vdim: int, value_tile: int, q_scale: float, k_scale: float, cap: float, chunked: bool,
-                  qk_share: int = 1) -> torch.Tensor:
+                  qk_share: int = 1, qkv_act: Optional[str] = None) -> torch.Tensor:
     """The matrix memories of csrc/matrix_memory.cu over the float rows `proj` whose columns hold q, k, v (and the gates' pre-activations) at the
     given offsets; state [slots, memory_slot_floats(..)] float32.  Without `decay` and without `zi_off` the column `zf_off` holds the log of the
-    factor a token and head; `qk_share` heads in a row read one query and key."""
+    factor a token and head; `qk_share` heads in a row read one query and key; `qkv_act` (sigmoid, silu, gelu_tanh, relu) acts on q, k and v as they are read."""
     base = _dev(proj, "proj", torch.float32)
     at = lambda off: None if off is None else base + 4 * off
-    check(lib().lb_matrix_memory_shared(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
+    check(lib().lb_matrix_memory_activated(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
                                  _opt(freq, "freq", torch.float32), rot_dims, _dev(positions, "positions", torch.int32), _dev(q_start, "q_start", torch.int32),
                                  _dev(slots, "slots", torch.int32), _dev(state, "state", torch.float32), state.stride(0), _dev(out, "out", torch.float32),
                                  out.stride(0), q_start.numel() - 1, n_head, dim, vdim, value_tile, float(q_scale), float(k_scale), float(cap), int(chunked),
-                                 int(qk_share), stream_ptr()), "matrix_memory")
+                                 int(qk_share), _QKV_ACT[qkv_act], stream_ptr()), "matrix_memory")
     return out
 
 
 def matrix_memory_pieces(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, zi_off: Optional[int], zf_off: Optional[int], decay: Optional[torch.Tensor],
                          freq: Optional[torch.Tensor], rot_dims: int, positions: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
                          out: torch.Tensor, n_head: int, dim: int, vdim: int, value_tile: int, q_scale: float, k_scale: float, cap: float,
-                         qk_share: int = 1) -> torch.Tensor:
+                         qk_share: int = 1, qkv_act: Optional[str] = None) -> torch.Tensor:
     """matrix_memory in its form for long portions: every piece of 32 rows a block of its own (three launches)."""
     base = _dev(proj, "proj", torch.float32)
     at = lambda off: None if off is None else base + 4 * off
@@ -737,11 +742,11 @@ def matrix_memory_pieces(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
     fn = lib().lb_matrix_memory_pieces_floats
     fn.argtypes, fn.restype = [_i] * 6, _c.c_int64
     scratch = torch.empty(int(fn(T, S, n_head, dim, vdim, value_tile)), dtype=torch.float32, device=proj.device)
-    check(lib().lb_matrix_memory_pieces_shared(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
+    check(lib().lb_matrix_memory_pieces_activated(at(q_off), at(k_off), at(v_off), at(zi_off), at(zf_off), proj.stride(0), _opt(decay, "decay", torch.float32),
                                         _opt(freq, "freq", torch.float32), rot_dims, _dev(positions, "positions", torch.int32),
                                         _dev(q_start, "q_start", torch.int32), _dev(slots, "slots", torch.int32), _dev(state, "state", torch.float32),
                                         state.stride(0), _dev(out, "out", torch.float32), out.stride(0), T, S, n_head, dim, vdim, value_tile, float(q_scale),
-                                        float(k_scale), float(cap), _dev(scratch, "scratch"), int(qk_share), stream_ptr()), "matrix_memory_pieces")
+                                        float(k_scale), float(cap), _dev(scratch, "scratch"), int(qk_share), _QKV_ACT[qkv_act], stream_ptr()), "matrix_memory_pieces")
     return out
 
 

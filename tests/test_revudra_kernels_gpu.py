@@ -228,6 +228,49 @@ def test_sublayer_output_normed_and_added_to_the_stream(dev, width, rows):
         assert np.abs(xs.double().cpu().numpy() - (x[:, :width] + m * y / np.sqrt((y * y).mean(-1, keepdims=True) + eps))).max() < 1e-5 * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("H,D,E,tile,act", [(3, 12, 20, 20, "silu"), (2, 32, 64, 32, "silu"), (1, 1, 1, 1, "sigmoid"), (4, 8, 33, 17, "silu"), (2, 64, 16, 16, "relu"), (2, 8, 5, 4, "sigmoid")])
+def test_memory_with_activated_queries_keys_and_values(dev, H, D, E, tile, act):
+    """S = g S + act(k) act(v)^T, o = S^T act(q) in all three forms of the recurrence (row by row, in pieces, a block a piece) from the same state:
+    three requests of unequal length in scrambled slots, value tiles that do not divide the head (padded columns must stay out of it)."""
+    from liyab_b200 import ops
+    rng = np.random.default_rng(H * 10 + D)
+    lens = [150, 1, 37]
+    T = sum(lens)
+    cols = 2 * H * D + H * E + 3
+    proj = rng.standard_normal((T, cols))
+    decay = rng.uniform(0.8, 0.999, H)
+    f = {"silu": lambda z: z / (1 + np.exp(-z)), "sigmoid": lambda z: 1 / (1 + np.exp(-z)), "relu": lambda z: np.maximum(z, 0)}[act]
+    q, k, v = (f(proj[:, :H * D]).reshape(T, H, D), f(proj[:, H * D:2 * H * D]).reshape(T, H, D), f(proj[:, 2 * H * D:2 * H * D + H * E]).reshape(T, H, E))
+    ref = np.zeros((T, H, E))
+    at = 0
+    for n in lens:
+        S = np.zeros((H, D, E))
+        for t in range(at, at + n):
+            S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+            ref[t] = np.einsum("hde,hd->he", S, q[t])
+        at += n
+    t32 = lambda a, ty=torch.float32: torch.tensor(np.asarray(a), dtype=ty, device=dev)
+    q_start = t32(np.concatenate([[0], np.cumsum(lens)]), torch.int32)
+    slots = t32([2, 0, 3], torch.int32)
+    positions = t32(np.concatenate([np.arange(n) for n in lens]), torch.int32)
+    floats = ops.memory_slot_floats(H, D, E, tile)
+    outs = []
+    for form in ("rows", "pieces", "blocks"):
+        state = torch.zeros(4, floats, device=dev)
+        out = torch.full((T, H * E), float("nan"), device=dev)
+        if form == "blocks":
+            ops.matrix_memory_pieces(t32(proj), 0, H * D, 2 * H * D, None, None, t32(decay), None, 0, positions, q_start, slots, state, out, H, D, E, tile, 1.0, 1.0, 0.0,
+                                     qkv_act=act)
+        else:
+            ops.matrix_memory(t32(proj), 0, H * D, 2 * H * D, None, None, t32(decay), None, 0, positions, q_start, slots, state, out, H, D, E, tile, 1.0, 1.0, 0.0,
+                              form == "pieces", qkv_act=act)
+        got = out.double().cpu().numpy().reshape(T, H, E)
+        assert np.abs(got - ref).max() < 2e-4 * max(1.0, np.abs(ref).max()), form
+        outs.append((got, state.double().cpu().numpy()))
+    for got, state in outs[1:]:          # the forms leave the same state behind
+        assert np.abs(state - outs[0][1]).max() < 2e-4 * max(1.0, np.abs(outs[0][1]).max())
+
+
 def test_activation_over_some_columns(dev):
     from liyab_b200 import ops
     rng = np.random.default_rng(3)
